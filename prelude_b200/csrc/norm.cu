@@ -1,0 +1,219 @@
+// RMSNorm and fused residual-add + RMSNorm.
+//
+//   y = x / sqrt(mean(x^2) + eps) * w          (all arithmetic in float32)
+//
+// The residual stream `res` is float32 in every mode.  The fused form does
+//   res += x ;  y = rmsnorm(res) * w
+// in one pass over the row, which is the reference's add+norm protocol
+// (crates/prelude-core/src/models/commons/linear.rs:471-488; kernels
+// crates/prelude-cuda/src/kernels/kernels_src/normalization/rmsnorm.cu:33-51, 230-355)
+// with the sum kept in 32-bit instead of being rounded to the model type.
+//
+// One block per row.  The block size depends on the row width only, so the
+// order of the reduction, and with it every bit of the result, is the same
+// whatever else is in the batch.
+#include "common.cuh"
+
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+    v = pb_warp_sum(v);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int i = 0; i < nwarp; ++i) total += smem[i];   // same order in every thread
+    __syncthreads();
+    return total;
+}
+
+template <typename TX, typename TY>
+__global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__ res, const float* __restrict__ w,
+                                   TY* __restrict__ y, int width, float eps) {
+    __shared__ float red[32];
+    size_t row = blockIdx.x;
+    float* r = res + row * width;
+    TY* out = y + row * width;
+    float ss = 0.f;
+    if (x != nullptr) {
+        const TX* xr = x + row * width;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = r[i] + pb_ld(xr + i);
+            r[i] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = r[i];
+            ss += v * v;
+        }
+    }
+    float total = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, r[i] * inv * w[i]);
+}
+
+// Four elements per thread and access, the row kept in registers between the
+// two passes.  width % 4 == 0, width <= 4 * blockDim * ITERS.
+template <typename TX, typename TY, int ITERS>
+__global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, float* __restrict__ res, const float* __restrict__ w,
+                                        TY* __restrict__ y, int width, float eps) {
+    __shared__ float red[32];
+    size_t row = blockIdx.x;
+    float4* r4 = reinterpret_cast<float4*>(res + row * width);
+    const int n4 = width >> 2;
+    float4 keep[ITERS];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            float4 v = r4[i];
+            if (x != nullptr) {
+                const TX* xr = x + row * width + 4 * (size_t)i;
+                if constexpr (sizeof(TX) == 2) {
+                    uint2 raw = *reinterpret_cast<const uint2*>(xr);
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+                    v.x += a.x; v.y += a.y; v.z += b.x; v.w += b.y;
+                } else {
+                    float4 a = *reinterpret_cast<const float4*>(xr);
+                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                }
+                r4[i] = v;
+            }
+            keep[it] = v;
+            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+        }
+    }
+    float total = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(total / (float)width + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            float4 v = keep[it], g = w4[i];
+            float o0 = v.x * inv * g.x, o1 = v.y * inv * g.y, o2 = v.z * inv * g.z, o3 = v.w * inv * g.w;
+            TY* out = y + row * width + 4 * (size_t)i;
+            if constexpr (sizeof(TY) == 2) {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
+                uint2 raw;
+                raw.x = *reinterpret_cast<uint32_t*>(&p0);
+                raw.y = *reinterpret_cast<uint32_t*>(&p1);
+                *reinterpret_cast<uint2*>(out) = raw;
+            } else {
+                *reinterpret_cast<float4*>(out) = make_float4(o0, o1, o2, o3);
+            }
+        }
+    }
+}
+
+static int norm_threads(int width) {
+    if (width <= 64) return 32;
+    if (width <= 512) return 64;
+    if (width <= 2048) return 128;
+    return 256;
+}
+
+template <typename TX, typename TY>
+static int launch_add_rmsnorm(const void* x, float* res, const float* w, void* y, int rows, int width, float eps,
+                              cudaStream_t stream) {
+    int threads = norm_threads(width);
+    bool vec = width % 4 == 0 && pb_aligned(res, 16) && pb_aligned(w, 16) && pb_aligned(y, 8 * sizeof(TY) / 2) &&
+               (x == nullptr || pb_aligned(x, 8 * sizeof(TX) / 2)) && width <= 4 * threads * 8;
+    if (vec) {
+        int iters = (width / 4 + threads - 1) / threads;
+        if (iters <= 2)
+            add_rmsnorm_vec4_kernel<TX, TY, 2><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+        else if (iters <= 4)
+            add_rmsnorm_vec4_kernel<TX, TY, 4><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+        else
+            add_rmsnorm_vec4_kernel<TX, TY, 8><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+    } else {
+        add_rmsnorm_kernel<TX, TY><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+    }
+    return 0;
+}
+
+// res[rows, width] float32 (updated in place when x is given); x may be null
+// (no add); w float32 [width]; y [rows, width] of type dtype.  x has type dtype.
+PB_API int pb_add_rmsnorm(const void* x, float* res, const float* w, void* y, int dtype, int rows, int width,
+                          float eps, cudaStream_t stream) {
+    PB_REQUIRE(rows >= 0 && width > 0, "add_rmsnorm: bad sizes rows=%d width=%d", rows, width);
+    PB_REQUIRE(res && w && y, "add_rmsnorm: null pointer");
+    if (rows == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T, (launch_add_rmsnorm<T, T>(x, res, w, y, rows, width, eps, stream)));
+    PB_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+// Final norm on chosen rows only: y[i] = rmsnorm(res[rows[i]] + x[rows[i]]) * w.
+// The residual stream is left as it is; only the rows whose logits are wanted
+// are normalised (the reference selects the last row of each request after the
+// final norm, crates/prelude-core/src/models/commons/mod.rs:227-243; the order
+// does not change the values).
+template <typename TX, typename TY>
+__global__ void gather_add_rmsnorm_kernel(const TX* __restrict__ x, const float* __restrict__ res,
+                                          const int32_t* __restrict__ rows, const float* __restrict__ w,
+                                          TY* __restrict__ y, int width, int n_rows_total, float eps) {
+    __shared__ float red[32];
+    const int src = rows[blockIdx.x];
+    TY* out = y + (size_t)blockIdx.x * width;
+    if (src < 0 || src >= n_rows_total) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, 0.f);
+        return;
+    }
+    const float* r = res + (size_t)src * width;
+    const TX* xr = x ? x + (size_t)src * width : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = r[i] + (xr ? pb_ld(xr + i) : 0.f);
+        ss += v * v;
+    }
+    float total = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = r[i] + (xr ? pb_ld(xr + i) : 0.f);
+        pb_st(out + i, v * inv * w[i]);
+    }
+}
+
+PB_API int pb_gather_add_rmsnorm(const void* x, const float* res, const int32_t* rows, const float* w, void* y,
+                                 int dtype, int n_out, int n_rows_total, int width, float eps, cudaStream_t stream) {
+    PB_REQUIRE(n_out >= 0 && width > 0 && n_rows_total >= 0, "gather_add_rmsnorm: bad sizes");
+    PB_REQUIRE(res && rows && w && y, "gather_add_rmsnorm: null pointer");
+    if (n_out == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T,
+        (gather_add_rmsnorm_kernel<T, T><<<n_out, norm_threads(width), 0, stream>>>(
+            (const T*)x, res, rows, w, (T*)y, width, n_rows_total, eps)));
+    PB_CHECK_LAUNCH("gather_add_rmsnorm");
+    return 0;
+}
+
+// Plain norm of a tensor of the model's own type (used by parts that are not
+// on the residual stream, and by the per-kernel tests).
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y, int width,
+                               float eps) {
+    __shared__ float red[32];
+    size_t row = blockIdx.x;
+    const T* xr = x + row * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = pb_ld(xr + i);
+        ss += v * v;
+    }
+    float total = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(y + row * width + i, pb_ld(xr + i) * inv * w[i]);
+}
+
+PB_API int pb_rmsnorm(const void* x, const float* w, void* y, int dtype, int rows, int width, float eps,
+                      cudaStream_t stream) {
+    PB_REQUIRE(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
+    PB_REQUIRE(x && w && y, "rmsnorm: null pointer");
+    if (rows == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T,
+        (rmsnorm_kernel<T><<<rows, norm_threads(width), 0, stream>>>((const T*)x, w, (T*)y, width, eps)));
+    PB_CHECK_LAUNCH("rmsnorm");
+    return 0;
+}

@@ -1,0 +1,132 @@
+"""The batch of one step, as the model's parts see it.
+
+``StepItem`` is the step function's input for one request: its next tokens,
+the position of the first of them, and the places (indices into these tokens)
+whose logits are wanted.  ``build_step_batch`` packs the items of a step into
+flat device arrays with one host-to-device copy.  The reference builds the same
+arrays in ``batch_mixed_paged`` (crates/prelude-core/src/engine/model_runner/paged_mixed.rs:32-117):
+packed tokens, positions, cumulative query lengths, context lengths and padded
+block tables; the slot of a token is not shipped but recomputed by the kernels
+from (request, position) and the block table.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepItem:
+    request_id: object
+    tokens: Sequence[int]
+    position_start: int
+    want: Sequence[int] = ()            # indices into ``tokens``
+
+
+@dataclass
+class LayerCache:
+    """What one entry of the run order reads and writes: pages of a cache
+    group, or per-request state, or nothing."""
+    kind: Optional[str] = None          # "kv" | "state" | None
+    group: int = -1
+    k_pages: Optional[torch.Tensor] = None     # [num_pages, page_size, n_kv_heads, head_dim]
+    v_pages: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None       # [max_slots, *shape]
+
+
+@dataclass
+class StepBatch:
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor             # [T] int32
+    positions: torch.Tensor             # [T] int32, absolute position of each token
+    token_seq: torch.Tensor             # [T] int32, index of the token's request in this batch
+    cu_q: torch.Tensor                  # [R + 1] int32
+    q_start: torch.Tensor               # [R] int32, position of the request's first token in this step
+    kv_len: torch.Tensor                # [R] int32, tokens in the cache after this step
+    state_slots: torch.Tensor           # [R] int32
+    logit_rows: torch.Tensor            # [W] int32, rows of the packed batch whose logits are wanted
+    block_tables: Dict[int, torch.Tensor]   # cache group -> [R, max_blocks] int32 (-1 where no page)
+    status: torch.Tensor                # [1] int32, raised by kernels that met a bad page or position
+    # host copies, for planning and for mixers that loop on the host
+    q_lens: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int32))
+    q_start_host: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int32))
+    kv_len_host: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int32))
+    state_slots_host: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int32))
+    max_q_len: int = 0
+    max_kv_len: int = 0
+    decode_only: bool = False
+    extras: Dict[str, object] = field(default_factory=dict)    # per-kernel plans made once per step
+
+
+def _ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def build_step_batch(items: Sequence[StepItem], block_tables: Dict[int, List[List[int]]],
+                     state_slots: Sequence[int], device: torch.device, vocab_size: int,
+                     max_positions: int, min_table_width: int = 1) -> StepBatch:
+    """Pack ``items``; ``block_tables[group][i]`` is the page list of item i in
+    that cache group (-1 for a page that a window has passed)."""
+    R = len(items)
+    if R == 0:
+        raise ValueError("a step needs at least one request")
+    q_lens = np.array([len(it.tokens) for it in items], dtype=np.int32)
+    if (q_lens <= 0).any():
+        raise ValueError("every request of a step brings at least one token")
+    T = int(q_lens.sum())
+    q_start = np.array([it.position_start for it in items], dtype=np.int32)
+    kv_len = q_start + q_lens
+    if (q_start < 0).any() or int(kv_len.max()) > max_positions:
+        raise ValueError(f"positions must lie in [0, {max_positions}); a request would reach {int(kv_len.max())}")
+    cu_q = np.zeros(R + 1, dtype=np.int32)
+    np.cumsum(q_lens, out=cu_q[1:])
+    tokens = np.concatenate([np.asarray(it.tokens, dtype=np.int64) for it in items])
+    if tokens.min() < 0 or tokens.max() >= vocab_size:
+        raise ValueError(f"token ids must lie in [0, {vocab_size})")
+    token_seq = np.repeat(np.arange(R, dtype=np.int32), q_lens)
+    positions = (np.arange(T, dtype=np.int32) - np.repeat(cu_q[:-1], q_lens)) + np.repeat(q_start, q_lens)
+    rows = []
+    for i, it in enumerate(items):
+        for wi in it.want:
+            if not 0 <= wi < q_lens[i]:
+                raise ValueError(f"request {it.request_id!r}: wanted place {wi} outside its {q_lens[i]} tokens")
+            rows.append(int(cu_q[i]) + int(wi))
+    logit_rows = np.asarray(rows, dtype=np.int32)
+    slots = np.asarray(list(state_slots), dtype=np.int32)
+    if slots.shape[0] != R:
+        raise ValueError("one state slot per request")
+
+    tables_np = {}
+    for g, tabs in block_tables.items():
+        width = max(min_table_width, max(len(t) for t in tabs))
+        arr = np.full((R, width), -1, dtype=np.int32)
+        for i, t in enumerate(tabs):
+            arr[i, :len(t)] = t
+        tables_np[g] = arr
+
+    # one pinned staging buffer, one copy
+    parts = [tokens.astype(np.int32), positions.astype(np.int32), token_seq, cu_q, q_start, kv_len, slots, logit_rows]
+    parts += [tables_np[g].reshape(-1) for g in sorted(tables_np)]
+    offsets = np.cumsum([0] + [p.size for p in parts])
+    flat = torch.empty(int(offsets[-1]) + 1, dtype=torch.int32, pin_memory=(device.type == "cuda"))
+    flat_np = flat.numpy()
+    for p, o in zip(parts, offsets[:-1]):
+        flat_np[o:o + p.size] = p
+    flat_np[-1] = 0                                   # the status word
+    dev = flat.to(device, non_blocking=True)
+
+    def cut(i):
+        return dev[int(offsets[i]):int(offsets[i + 1])]
+
+    tables_dev = {}
+    for n, g in enumerate(sorted(tables_np)):
+        tables_dev[g] = cut(8 + n).view(R, tables_np[g].shape[1])
+    return StepBatch(
+        n_tokens=T, n_seqs=R, token_ids=cut(0), positions=cut(1), token_seq=cut(2), cu_q=cut(3), q_start=cut(4),
+        kv_len=cut(5), state_slots=cut(6), logit_rows=cut(7), block_tables=tables_dev, status=dev[-1:],
+        q_lens=q_lens, q_start_host=q_start, kv_len_host=kv_len, state_slots_host=slots,
+        max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()))

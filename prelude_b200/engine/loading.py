@@ -1,0 +1,58 @@
+"""From a model folder to a model on the device with its cache and runner.
+
+The order is the reference's (crates/prelude-core/src/engine/loading.rs:34-75,
+165-264): read config.json, resolve the architecture through the registry,
+open the safetensors files, build the model from its parts, size the cache.
+"""
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import load_model_config
+from ..config.spec import ModelSpec
+from ..parts.model import DecoderModel
+from ..parts.registry import RunContext
+from ..weights.loader import WeightStore
+from .runner import ModelRunner
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
+           "fp32": torch.float32}
+
+
+def parse_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype in (torch.bfloat16, torch.float32):
+            return dtype
+        raise ValueError(f"dtype must be bfloat16 or float32, not {dtype}")
+    try:
+        return _DTYPES[dtype.lower()]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {dtype!r}") from None
+
+
+def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
+               device: Union[str, torch.device] = "cuda:0") -> DecoderModel:
+    """config.json -> registry -> typed configuration -> model spec -> parts -> weights by name."""
+    config = load_model_config(model_dir)
+    store = WeightStore.open(model_dir)
+    return build_model(config.to_model_spec(), store, dtype, device)
+
+
+def build_model(spec: ModelSpec, store: WeightStore, dtype: Union[str, torch.dtype] = "bfloat16",
+                device: Union[str, torch.device] = "cuda:0") -> DecoderModel:
+    ctx = RunContext(torch.device(device), parse_dtype(dtype))
+    return DecoderModel(spec).load(store, ctx)
+
+
+def make_runner(model: DecoderModel, page_size: int = 16, num_pages: Optional[int] = None,
+                max_tokens: Optional[int] = None, max_slots: int = 256) -> ModelRunner:
+    """A cache of ``num_pages`` pages (or enough for ``max_tokens`` tokens) and the runner over it."""
+    if num_pages is None:
+        if max_tokens is None:
+            raise ValueError("give num_pages or max_tokens")
+        num_pages = -(-max_tokens // page_size)
+    cache = CacheManager(model.cache_needs(), page_size, num_pages, max_slots, model.ctx.device, model.ctx.dtype)
+    return ModelRunner(model, cache)

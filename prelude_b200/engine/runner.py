@@ -1,0 +1,109 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step`` takes, for each request of the step, its next tokens and
+the places among them whose logits are wanted.  Portions of prompts stand
+beside single decoded tokens, cut anywhere.  It makes room in the cache, packs
+the batch, runs only the tokens it was given against the cache that earlier
+steps left, and returns float32 logits for the wanted places, in the order of
+the entries and of their ``want`` lists.  A request's position is how many of
+its tokens the cache already holds.
+
+It is the reference's ``batch_mixed_paged``
+(crates/prelude-core/src/engine/model_runner/paged_mixed.rs:13-335) with two
+differences: logits come back for any wanted place instead of the last row of
+every request, and room in the cache is made here rather than by the caller.
+Trace replay, the scheduler and the tests all go through this one function.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..ops.library import KernelLibraryError, require_device
+from ..parts.model import DecoderModel
+from .batch import StepBatch, StepItem, build_step_batch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step."""
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepError(RuntimeError):
+    """A kernel reported a bad page or position during the step."""
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager):
+        require_device()
+        self.model, self.cache = model, cache
+        self.device = model.ctx.device
+        self.caches = cache.layer_caches(len(model.order))
+        self.steps_run = 0
+        self.last_batch: Optional[StepBatch] = None
+
+    # -- room in the cache --------------------------------------------------------------
+    def reserve(self, entries: Sequence[StepEntry]) -> List[int]:
+        """Register new requests and grow every entry's cache to hold its tokens.
+        All or nothing: raises OutOfPages before anything is taken when the
+        step as a whole does not fit.  Returns each entry's start position."""
+        cache = self.cache
+        seen = set()
+        demand: Dict[int, int] = {}
+        new_requests = 0
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            live = cache.has_request(e.request_id)
+            new_requests += 0 if live else 1
+            start = cache.tokens_of(e.request_id) if live else 0
+            for gid, n in cache.pages_needed(e.request_id if live else None, start + len(e.tokens)).items():
+                demand[gid] = demand.get(gid, 0) + n
+        for gid, n in demand.items():
+            free = cache.groups[gid].allocator.num_free
+            if n > free:
+                raise OutOfPages(f"the step needs {n} new pages in cache group {gid}, {free} of {cache.num_pages} are free")
+        if new_requests > cache.slots.num_free:
+            raise OutOfPages(f"the step starts {new_requests} requests, {cache.slots.num_free} state slots are free")
+        starts = []
+        for e in entries:
+            if not cache.has_request(e.request_id):
+                cache.add_request(e.request_id)
+            start = cache.tokens_of(e.request_id)
+            cache.grow(e.request_id, start + len(e.tokens))
+            starts.append(start)
+        return starts
+
+    # -- the step -----------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], check_status: bool = True) -> torch.Tensor:
+        starts = self.reserve(entries)
+        items = [StepItem(e.request_id, e.tokens, s, e.want) for e, s in zip(entries, starts)]
+        rids = [e.request_id for e in entries]
+        spec = self.model.spec
+        batch = build_step_batch(items, self.cache.block_tables(rids), [self.cache.slot_of(r) for r in rids],
+                                 self.device, spec.vocab_size, spec.max_positions)
+        self.cache.zero_fresh_state()
+        logits = self.model.forward(batch, self.caches)
+        for r in rids:
+            self.cache.trim(r)
+        self.steps_run += 1
+        self.last_batch = batch
+        if check_status:
+            code = int(batch.status.item())
+            if code != 0:
+                raise StepError(f"a kernel met a bad page id or position during the step (code {code})")
+        return logits
+
+    def finish(self, request_id: Hashable) -> None:
+        """The request has ended: what it holds goes back to the pools."""
+        self.cache.release(request_id)

@@ -1,0 +1,51 @@
+"""Gated feed-forward: down(act(gate(x)) * up(x)), no biases
+(crates/prelude-core/src/models/qwen3.rs:383-448).
+
+Gate and up rows are stored one below the other so that one product feeds the
+activation kernel; the reference merges them the same way where its kernels
+take the merged layout (qwen3.rs:411-419).  The activation comes from the spec;
+the reference parses ``hidden_act`` and then applies SiLU regardless.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.spec import GatedMlpSpec
+from ..ops import kernels as K
+from ..ops.linear import linear
+from ..weights.loader import TensorReq
+from .registry import RunContext, register_part
+
+_ACTIVATIONS = {"silu": K.silu_mul}
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMlp:
+    def __init__(self, spec: GatedMlpSpec, prefix: str):
+        if spec.activation not in _ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: no kernel for activation {spec.activation!r}; known: {sorted(_ACTIVATIONS)}")
+        self.spec, self.prefix = spec, prefix
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self) -> Dict[str, TensorReq]:
+        s, p = self.spec, self.prefix
+        return {
+            f"{p}.gate_proj.weight": TensorReq((s.intermediate_size, s.hidden_size)),
+            f"{p}.up_proj.weight": TensorReq((s.intermediate_size, s.hidden_size)),
+            f"{p}.down_proj.weight": TensorReq((s.hidden_size, s.intermediate_size)),
+        }
+
+    def load(self, get, ctx: RunContext) -> None:
+        p = self.prefix
+
+        def mat(name):
+            return get(f"{p}.{name}").to(device=ctx.device, dtype=ctx.dtype)
+
+        self.w_gate_up = torch.cat([mat("gate_proj.weight"), mat("up_proj.weight")], dim=0).contiguous()
+        self.w_down = mat("down_proj.weight").contiguous()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate_up = linear(x, self.w_gate_up)
+        return linear(_ACTIVATIONS[self.spec.activation](gate_up), self.w_down)

@@ -1,0 +1,101 @@
+"""The engine against the plain implementation, on the GPU, in 32-bit and in
+bfloat16: whole requests, a decoded tail, changing portions, and mixed batches
+with so few pages that they are used again."""
+import pytest
+import torch
+
+import harness
+import tiny
+from plain.qwen3_plain import forward_logits
+
+pytestmark = pytest.mark.gpu
+
+# bfloat16 has 8 bits of mantissa; through a few layers the logits of these
+# models stay within 3% of their largest magnitude.  32-bit differs from the
+# plain implementation by summation order only.
+TOL = {torch.float32: (1e-4, 0.0), torch.bfloat16: (0.0, 3e-2)}
+
+REQUESTS = {
+    "A": {"a1": 1, "a5": 5, "a17": 17, "a70": 70},
+    "B": {"b2": 2, "b9": 9, "b31": 31, "b64": 64, "b150": 150},
+    "C": {"c40": 40, "c33": 33, "c129": 129},
+}
+
+
+def _requests(which):
+    cfg = tiny.PARAMS[which][0]
+    return {rid: tiny.random_ids(n, cfg["vocab_size"], sum(map(ord, rid))) for rid, n in REQUESTS[which].items()}
+
+
+def _reference(which, folder, reqs):
+    cfg = tiny.PARAMS[which][0]
+    w = tiny.read_weights(folder)
+    return {rid: forward_logits(cfg, w, toks) for rid, toks in reqs.items()}
+
+
+def _compare(got, ref, dtype):
+    atol, rel = TOL[dtype]
+    worst = 0.0
+    for (rid, pos), row in got.items():
+        want = ref[rid][pos]
+        bound = atol + rel * float(want.abs().max())
+        diff = float((row - want).abs().max())
+        worst = max(worst, diff / bound)
+        assert diff <= bound, f"request {rid} position {pos}: max diff {diff:.3e} > {bound:.3e}"
+    return worst
+
+
+def _runner(folder, dtype, page_size, num_pages):
+    from prelude_b200.engine.loading import load_model, make_runner
+    model = load_model(folder, dtype, "cuda:0")
+    return make_runner(model, page_size=page_size, num_pages=num_pages, max_slots=8)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    out = {}
+    for which in "ABC":
+        for dtype in (torch.float32, torch.bfloat16):
+            out[(which, dtype)] = tiny.make_folder(root, which, dtype)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
+def test_cuts_match_plain(folders, which, dtype, cut):
+    folder = folders[(which, dtype)]
+    reqs = _requests(which)
+    ref = _reference(which, folder, reqs)
+    page = tiny.PARAMS[which][2]
+    schedule = {"whole": harness.whole, "tail_decode": harness.tail_decode, "portions": harness.portions,
+                "mixed": harness.mixed}[cut](reqs)
+    need = harness.peak_tokens(schedule, page)
+    total = sum(-(-len(t) // page) for t in reqs.values())
+    num_pages = need // page                      # exactly what the busiest moment needs
+    if cut == "mixed":
+        assert num_pages < total, "the pool must be smaller than the sum of all requests, so pages are used again"
+    runner = _runner(folder, dtype, page, num_pages)
+    got = harness.run_schedule(runner, schedule)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _compare(got, ref, dtype)
+    runner.cache.check()
+    assert runner.cache.used_pages() == 0 and not runner.cache.requests
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_f32_cuts_agree_bitwise(folders, which):
+    """In 32-bit every kernel sums in an order that depends on the row alone, so
+    all ways of cutting give the same bits."""
+    folder = folders[(which, torch.float32)]
+    reqs = _requests(which)
+    page = tiny.PARAMS[which][2]
+    results = []
+    for cut in (harness.whole, harness.tail_decode, harness.portions, harness.mixed):
+        schedule = cut(reqs)
+        runner = _runner(folder, torch.float32, page, harness.peak_tokens(schedule, page) // page)
+        results.append(harness.run_schedule(runner, schedule))
+    for other in results[1:]:
+        for key, row in results[0].items():
+            assert torch.equal(row, other[key]), f"{key}: cuts disagree by {(row - other[key]).abs().max():.3e}"
