@@ -1,0 +1,228 @@
+"""The Python entry point: ``Engine(model_dir).generate(prompts, ...)``.
+
+The reference has no Python binding; the shape follows its engine interface
+(``InferenceEngine::generate``, crates/prelude-core/src/engine/mod.rs:76-132)
+and its request and result records (crates/prelude-core/src/types.rs:400-434):
+a request is token ids plus sampling options, a result is the generated ids, a
+finish reason, token counts and timings.  Option names and defaults are those
+of the reference's command line (crates/prelude-server/src/main.rs:15-183).
+
+``generate`` runs the reference's loop (crates/prelude-core/src/engine/run/ar.rs:205-387):
+schedule a step, build the batch, run it, sample where a request reached its
+last token, apply the stop checks, free what finished.  Tokenisation lies
+outside: prompts are token ids.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import load_model_config
+from ..ops.library import require_device
+from ..sampling.sampler import Sampler
+from .loading import load_model, parse_dtype
+from .runner import ModelRunner, StepEntry
+from .scheduler import CachePoolView, SamplingParams, Scheduler, SchedulerConfig
+
+
+@dataclass
+class GenerateResult:
+    request_id: object
+    token_ids: List[int]
+    finish_reason: str                  # "eos" | "stop" | "length" | "abort" | "cache_full"
+    prompt_tokens: int
+    completion_tokens: int
+    ttft_ms: float = 0.0                # first token after the request was handed in
+    total_ms: float = 0.0
+    preemptions: int = 0
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    decode_steps: int = 0
+    graph_steps: int = 0
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+    pages_total: int = 0
+    pages_in_use_peak: int = 0
+    step_ms_total: float = 0.0
+
+
+def _activation_reserve_bytes(spec, max_tokens: int, max_rows: int) -> int:
+    """A generous bound on what one step allocates beside weights and cache."""
+    widest = 0
+    for b in spec.blocks:
+        m, f = b.mixer, b.feed_forward
+        qkv = getattr(m, "num_heads", 0) * getattr(m, "head_dim", 0) + 2 * getattr(m, "num_kv_heads", 0) * getattr(m, "head_dim", 0)
+        widest = max(widest, 4 * spec.hidden_size * 4 + 4 * qkv * 2 + 6 * getattr(f, "intermediate_size", 0) * 2)
+    return max_tokens * widest + 3 * max_rows * spec.vocab_size * 4 + (1 << 30)
+
+
+class Engine:
+    def __init__(self, model: str, dtype: str = "bf16", device: str = "cuda:0", page_size: int = 16,
+                 num_pages: Optional[int] = None, gpu_memory_utilization: float = 0.9,
+                 max_running_requests: int = 256, max_num_batched_tokens: int = 8192,
+                 long_prefill_token_threshold: int = 0, max_total_tokens: int = 0, decode_reservation_cap: int = 0,
+                 decode_priority_max_remaining_tokens: int = 4, cuda_graph: bool = True, cuda_graph_max_bs: int = 64,
+                 max_model_len: Optional[int] = None):
+        """``model`` is a folder with config.json and safetensors files.
+
+        ``num_pages`` fixes the cache size; without it the cache takes what
+        ``gpu_memory_utilization`` of the device leaves after the weights and a
+        reserve for one step's activations
+        (crates/prelude-core/src/scheduler/components/cache/manager.rs:240-280).
+        ``max_model_len`` caps a request's length below max_position_embeddings.
+        """
+        require_device()
+        self.device = torch.device(device)
+        self.dtype = parse_dtype(dtype)
+        self.config = load_model_config(model)
+        self.model = load_model(model, self.dtype, self.device)
+        spec = self.model.spec
+        self.max_model_len = min(max_model_len or spec.max_positions, spec.max_positions)
+        needs = self.model.cache_needs()
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        if num_pages is None:
+            per_page = max(1, CacheManager.bytes_per_page(needs, page_size, elem))
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = free - int((1.0 - gpu_memory_utilization) * total) \
+                - _activation_reserve_bytes(spec, max_num_batched_tokens, max_running_requests)
+            num_pages = max(16, budget // per_page)
+            # no more than every request slot at full length could use
+            num_pages = min(num_pages, max_running_requests * -(-self.max_model_len // page_size))
+        self.cache = CacheManager(needs, page_size, int(num_pages), max_running_requests, self.device, self.dtype)
+        self.runner = ModelRunner(self.model, self.cache)
+        self.sched_config = SchedulerConfig(
+            max_running_requests=max_running_requests, max_num_batched_tokens=max_num_batched_tokens,
+            long_prefill_token_threshold=long_prefill_token_threshold, max_total_tokens=max_total_tokens,
+            decode_reservation_cap=decode_reservation_cap or self.max_model_len,
+            decode_priority_max_remaining_tokens=decode_priority_max_remaining_tokens, page_size=page_size)
+        self.sampler = Sampler(self.device)
+        self.eos_token_ids = tuple(spec.eos_token_ids)
+        self.cuda_graph = cuda_graph
+        self.cuda_graph_max_bs = cuda_graph_max_bs
+        self._graphs = None
+        self._stats = EngineStats(pages_total=int(num_pages))
+        self._next_id = 0
+
+    # -- the raw step function, for tests and tools ---------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        return self.runner.step(entries)
+
+    def finish(self, request_id) -> None:
+        self.runner.finish(request_id)
+
+    def stats(self) -> EngineStats:
+        return self._stats
+
+    # -- generation ---------------------------------------------------------------------
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+                 sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None, *,
+                 max_new_tokens: Optional[int] = None, temperature: Optional[float] = None,
+                 top_p: Optional[float] = None, top_k: Optional[int] = None, seed: Optional[int] = None,
+                 stop_token_ids: Optional[Sequence[int]] = None, ignore_eos: Optional[bool] = None
+                 ) -> Union[GenerateResult, List[GenerateResult]]:
+        """Generate for one prompt (a list of token ids) or several (a list of
+        lists).  ``sampling`` gives the options per request or for all; keyword
+        options override it."""
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        plist = [list(prompts)] if single else [list(p) for p in prompts]
+        if isinstance(sampling, SamplingParams) or sampling is None:
+            plist_params = [sampling or SamplingParams()] * len(plist)
+        else:
+            plist_params = list(sampling)
+            if len(plist_params) != len(plist):
+                raise ValueError("one SamplingParams per prompt")
+        params = []
+        for p in plist_params:
+            q = SamplingParams(**vars(p))
+            for k, v in (("max_new_tokens", max_new_tokens), ("temperature", temperature), ("top_p", top_p),
+                         ("top_k", top_k), ("seed", seed), ("ignore_eos", ignore_eos)):
+                if v is not None:
+                    setattr(q, k, v)
+            if stop_token_ids is not None:
+                q.stop_token_ids = tuple(stop_token_ids)
+            params.append(q)
+        results = self._run(plist, params)
+        return results[0] if single else results
+
+    def _run(self, prompts: List[List[int]], params: List[SamplingParams]) -> List[GenerateResult]:
+        sched = Scheduler(self.sched_config, CachePoolView(self.cache))
+        t0 = time.perf_counter()
+        ids = []
+        first_token_at: Dict[object, float] = {}
+        vocab = self.model.spec.vocab_size
+        for prompt, p in zip(prompts, params):
+            if any((not isinstance(t, int)) or t < 0 or t >= vocab for t in prompt):
+                raise ValueError(f"prompt token ids must be integers in [0, {vocab})")
+            rid = self._next_id
+            self._next_id += 1
+            sched.add_request(rid, prompt, p, self.max_model_len)
+            ids.append(rid)
+        done: Dict[object, GenerateResult] = {}
+        while sched.has_work():
+            items = sched.schedule()
+            self._collect(sched, done, first_token_at, t0)
+            if not items:
+                if sched.has_work():
+                    raise RuntimeError("the scheduler has work but could schedule nothing")
+                break
+            tokens = self._run_step(items)
+            now = time.perf_counter()
+            for it, tok in zip(items, tokens):
+                if tok is not None and it.seq.request_id not in first_token_at:
+                    first_token_at[it.seq.request_id] = now
+                sched.on_step_done(it, tok, self.eos_token_ids)
+            self._collect(sched, done, first_token_at, t0)
+        self._stats.preemptions += sched.stats["preemptions"]
+        return [done[r] for r in ids]
+
+    def _collect(self, sched: Scheduler, done, first_token_at, t0) -> None:
+        now = time.perf_counter()
+        for seq in sched.drain_finished():
+            done[seq.request_id] = GenerateResult(
+                seq.request_id, list(seq.output), seq.finish_reason or "abort", len(seq.prompt), len(seq.output),
+                ttft_ms=(first_token_at.get(seq.request_id, now) - t0) * 1e3, total_ms=(now - t0) * 1e3,
+                preemptions=seq.preempt_count)
+
+    def _run_step(self, items) -> List[Optional[int]]:
+        """Run one scheduled step; returns the sampled token per item (None
+        where the portion did not reach the request's end)."""
+        t0 = time.perf_counter()
+        entries, rows = [], []
+        for it in items:
+            toks = it.seq.tokens[it.start:it.start + it.n_tokens]
+            entries.append(StepEntry(it.seq.request_id, toks, [it.n_tokens - 1] if it.samples else []))
+            if it.samples:
+                rows.append(it)
+        decode_only = all(it.n_tokens == 1 for it in items)
+        logits = self.runner.step(entries, check_status=False)
+        sampled = self.sampler.sample(
+            logits, [it.seq.params.temperature for it in rows], [it.seq.params.top_k for it in rows],
+            [it.seq.params.top_p for it in rows], [it.seq.params.seed for it in rows],
+            [len(it.seq.output) for it in rows]) if rows else []
+        code = int(self.runner.last_batch.status.item())
+        if code != 0:
+            raise RuntimeError(f"a kernel met a bad page id or position during the step (code {code})")
+        st = self._stats
+        st.steps += 1
+        st.decode_steps += 1 if decode_only else 0
+        st.generated_tokens += len(rows)
+        st.prompt_tokens += sum(it.n_tokens for it in items if it.seq.prefilling and it.start < len(it.seq.prompt))
+        st.pages_in_use_peak = max(st.pages_in_use_peak, self.cache.used_pages())
+        st.step_ms_total += (time.perf_counter() - t0) * 1e3
+        out: List[Optional[int]] = []
+        k = 0
+        for it in items:
+            if it.samples:
+                out.append(int(sampled[k]))
+                k += 1
+            else:
+                out.append(None)
+        return out
