@@ -114,7 +114,9 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
     ``qkv`` is the merged projection [T, (nH + 2 nKV) D] (or [T, nH D] when
     nothing is written).  Pages are [num_pages, page_size, nKV, D].
     """
-    _need(qkv, "qkv")
+    _need(qkv, "qkv", contiguous=False)
+    if qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelLibraryError("qknorm_rope_kvwrite: the projection must be [tokens, columns] with dense rows")
     T = qkv.shape[0]
     q_cols, kv_cols = n_heads * head_dim, n_kv_heads * head_dim
     want = q_cols + (2 * kv_cols if write_kv else 0)
