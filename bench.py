@@ -1,0 +1,298 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--layers L] [--impl ours|reference]
+
+The default run has the layer sizes of Qwen3-4B (BASELINE.json configs[2]) with
+random weights in bfloat16, a batch of 8 requests that each hold a 2,048-token
+prefix in a cache laid out for 4,096-token contexts with 16-token pages, and
+prints one JSON line:
+
+  value     decoded tokens a second, timed on the device: K replays of the captured
+            decode step (model + sampling, the sampled token fed back on the device)
+            between two CUDA events;
+  e2e       the same through Engine.generate(): host token ids in, host token ids
+            out, every step's inputs copied from pinned memory and its tokens read back;
+  prefill   one 2,048-token prompt through the step function;
+  roofline  the bytes a decode step has to read (every weight once, the cache of
+            the live requests) over its time, against the measured copy bandwidth;
+  points    the device-timed value at batch 1 and 64.
+
+Every decode step reads the whole model (8 GB at full size), far more than the
+126 MB L2, so no flush is needed between steps ("l2": "inputs_exceed_l2").
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=2560,
+                intermediate_size=9728, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, max_position_embeddings=40960, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=True, attention_bias=False, use_sliding_window=False, hidden_act="silu")
+CONTEXT_LEN, PREFIX_LEN, PAGE_SIZE, PREFILL_TOKENS = 4096, 2048, 16, 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        out = dict(FALLBACK_PEAKS, source="measured")
+        for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if isinstance(raw.get(k), (int, float)) and raw[k] > 0:
+                out[k] = float(raw[k])
+        return out
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed regions run."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), [p.strip() for p in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows):
+        rows = [p for t, p in self.samples if any(a <= t <= b for a, b in windows) and len(p) >= 6]
+        if not rows:
+            rows = [p for _, p in self.samples if len(p) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        mhz = [int(float(p[0])) for p in rows if p[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for p in rows for n, v in zip(names, p[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
+                "sm_max_mhz": int(float(rows[0][1])) if rows[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def build_engine(layers, max_running, num_pages):
+    import torch
+    from prelude_b200 import Engine
+    from prelude_b200.config import load_model_config
+    from prelude_b200.engine.loading import build_model
+    from prelude_b200.weights.loader import WeightStore
+    from prelude_b200.weights.random_init import random_tensors
+    cfg = dict(QWEN3_4B, num_hidden_layers=layers)
+    tensors = random_tensors(cfg, seed=0, std=0.02, norm_jitter=0.05, dtype=torch.bfloat16, device="cuda:0")
+    model = build_model(load_model_config(cfg).to_model_spec(), WeightStore.from_tensors(tensors), "bf16", "cuda:0")
+    del tensors
+    torch.cuda.empty_cache()
+    return Engine(model, page_size=PAGE_SIZE, num_pages=num_pages, max_running_requests=max_running,
+                  max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN, cuda_graph=True, cuda_graph_max_bs=64), cfg
+
+
+def weight_bytes_per_step(cfg):
+    """Bytes of weights one decode step reads: every matrix once (the tied
+    embedding table once, as the output head), norm scales in float32."""
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    per_layer = 2 * (qkv * H + H * cfg["num_attention_heads"] * cfg["head_dim"] + 3 * I * H) + 4 * (2 * H + 2 * cfg["head_dim"])
+    head = 2 * cfg["vocab_size"] * H * (1 if cfg["tie_word_embeddings"] else 1)
+    return L * per_layer + head + 4 * H
+
+
+def kv_bytes_per_token(cfg):
+    return 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg, T):
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    nH, D = cfg["num_attention_heads"], cfg["head_dim"]
+    qkv = (nH + 2 * cfg["num_key_value_heads"]) * D
+    gemm = 2 * T * L * (qkv * H + H * nH * D + 3 * I * H) + 2 * 1 * cfg["vocab_size"] * H
+    attn = L * 4 * nH * D * (T * (T + 1) // 2)          # QK^T and PV over the causal half
+    return gemm + attn
+
+
+def time_decode(engine, cfg, batch, steps, warmup, seed):
+    """Device time of ``steps`` decode steps at ``batch`` requests with PREFIX_LEN-token prefixes."""
+    import torch
+    from prelude_b200.engine.graph import DecodeGraph
+    from prelude_b200.engine.runner import StepEntry
+    from prelude_b200.ops import library
+    runner, cache = engine.runner, engine.cache
+    g = torch.Generator().manual_seed(seed)
+    rids = [f"bench{seed}_{i}" for i in range(batch)]
+    for rid in rids:                                     # real prefill fills the cache
+        ids = torch.randint(0, cfg["vocab_size"], (PREFIX_LEN,), generator=g).tolist()
+        runner.step([StepEntry(rid, ids, [])], check_status=False)
+    total = PREFIX_LEN + warmup + steps + 1
+    for rid in rids:                                     # room for every token the loop will write
+        cache.grow(rid, total)
+    cache.flush_table_updates()
+    graph = DecodeGraph(runner, batch, self_feeding=True)
+    tokens = torch.randint(0, cfg["vocab_size"], (batch,), generator=g).tolist()
+    graph.load(tokens, [PREFIX_LEN] * batch, [cache.slot_of(r) for r in rids], [0.0] * batch, [0] * batch, [0] * batch)
+    graph.capture()
+    graph.load(tokens, [PREFIX_LEN] * batch, [cache.slot_of(r) for r in rids], [0.0] * batch, [0] * batch, [0] * batch)
+    for _ in range(warmup):
+        graph.replay()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    start.record()
+    for _ in range(steps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = start.elapsed_time(end)
+    status = int(graph.status.item())
+    if status != 0:
+        raise RuntimeError(f"decode loop raised kernel status {status}")
+    for rid in rids:
+        runner.finish(rid)
+    del graph
+    avg_ctx = PREFIX_LEN + warmup + (steps + 1) / 2.0
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches_per_step": None,
+            "avg_ctx": avg_ctx, "window": (t0, t1)}, library
+
+
+def time_prefill(engine, cfg, warmup, reps=3):
+    import torch
+    from prelude_b200.engine.runner import StepEntry
+    runner = engine.runner
+    g = torch.Generator().manual_seed(7)
+    times = []
+    t0 = time.time()
+    for i in range(warmup + reps):
+        ids = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        runner.step([StepEntry(f"prefill{i}", ids, [PREFILL_TOKENS - 1])], check_status=False)
+        e.record()
+        torch.cuda.synchronize()
+        runner.finish(f"prefill{i}")
+        if i >= warmup:
+            times.append(s.elapsed_time(e))
+    return min(times), (t0, time.time())
+
+
+def time_e2e(engine, cfg, batch, steps):
+    """Decoded tokens a second through Engine.generate(): after each request's first token."""
+    import torch
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg["vocab_size"], (PREFIX_LEN,), generator=g).tolist() for _ in range(batch)]
+    engine.generate(prompts[:1], temperature=0.0, max_new_tokens=4, ignore_eos=True)          # warm: captures, allocator
+    t0 = time.time()
+    res = engine.generate(prompts, temperature=0.0, max_new_tokens=steps + 1, ignore_eos=True)
+    t1 = time.time()
+    decode_ms = max(r.total_ms for r in res) - max(r.ttft_ms for r in res)
+    toks = sum(r.completion_tokens - 1 for r in res)
+    gr = engine.graphs.get(batch)
+    return {"value": toks / (decode_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": gr.h2d_bytes,
+            "d2h_bytes_per_step": gr.d2h_bytes, "decode_ms": decode_ms}, (t0, t1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace with git-only dependencies; no cargo/rustc and no network here, "
+                          "so it cannot be built or installed offline"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus N with N > 1 is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+    import torch
+    pk = peaks()
+    # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages
+    biggest = 64 if not args.no_points else args.batch
+    pages_per_req = -(-(PREFIX_LEN + args.warmup + args.steps + 2) // PAGE_SIZE)
+    num_pages = max(biggest, args.batch) * pages_per_req + 2 * (PREFILL_TOKENS // PAGE_SIZE) + 8
+    engine, cfg = build_engine(args.layers, max(64, args.batch) + 2, num_pages)
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+
+    prefill_ms, w = time_prefill(engine, cfg, args.warmup)
+    windows.append(w)
+    dec, library = time_decode(engine, cfg, args.batch, args.steps, args.warmup, seed=1)
+    windows.append(dec["window"])
+    points = {}
+    if not args.no_points:
+        for b, k in ((1, min(args.steps, 128)), (64, min(args.steps, 64))):
+            if b == args.batch:
+                points[f"decode_b{b}"] = round(dec["tok_s"], 1)
+                continue
+            d, _ = time_decode(engine, cfg, b, k, args.warmup, seed=100 + b)
+            windows.append(d["window"])
+            points[f"decode_b{b}"] = round(d["tok_s"], 1)
+    e2e, w = time_e2e(engine, cfg, args.batch, args.steps)
+    windows.append(w)
+    clocks.stop()
+
+    launches_per_step = engine.graphs.get(args.batch).launches
+    step_bytes = weight_bytes_per_step(cfg) + args.batch * dec["avg_ctx"] * kv_bytes_per_token(cfg)
+    achieved = step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
+    pf = prefill_flops(cfg, PREFILL_TOKENS)
+    line = {
+        "metric": "decode tok/s (Qwen3-4B sizes, random weights, bf16, batch 8, 2,048-token prefixes)",
+        "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dec["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "qwen3-4b-sizes", "layers": args.layers, "layers_full": QWEN3_4B["num_hidden_layers"],
+                   "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
+                   "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "vocab_size": cfg["vocab_size"], "tie_word_embeddings": True,
+                   "global_batch": args.batch, "seq_len": PREFIX_LEN, "context_len": CONTEXT_LEN,
+                   "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single",
+                   "l2": "inputs_exceed_l2", "peaks": pk["source"]},
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items() if k != "decode_ms"},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(pf / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(windows),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -57,10 +57,13 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, needs: Sequence[object], page_size: int, num_pages: int, max_slots: int,
-                 device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16):
+                 device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16,
+                 max_request_tokens: Optional[int] = None):
         """``needs[n]`` is the cache need of entry n of the run order (None for
         an entry without a cache of its own).  Every group gets ``num_pages`` pages
-        of ``page_size`` tokens."""
+        of ``page_size`` tokens.  With ``max_request_tokens`` every group also keeps
+        its block tables on the device, one row per state slot, updated entry by
+        entry (captured decode steps read those)."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size, self.num_pages, self.max_slots = page_size, num_pages, max_slots
@@ -88,8 +91,15 @@ class CacheManager:
         self.slots = SlotAllocator(max_slots)
         self.requests: Dict[Hashable, RequestCache] = {}
         self._fresh_slots: List[int] = []
+        self.table_width = _ceil_div(max_request_tokens, page_size) if max_request_tokens else 0
+        self.device_tables: Dict[int, torch.Tensor] = {}
+        self._table_updates: Dict[int, List[tuple]] = {}
         if device is not None:
             self._allocate_tensors()
+            if self.table_width:
+                for g in self.groups:
+                    self.device_tables[g.gid] = torch.full((max_slots, self.table_width), -1, dtype=torch.int32, device=device)
+                    self._table_updates[g.gid] = []
 
     # -- device memory ----------------------------------------------------------------
     def _allocate_tensors(self) -> None:
@@ -163,7 +173,11 @@ class CacheManager:
                 raise OutOfPages(f"request {rid!r} needs {n} more pages in cache group {gid} for {n_tokens} tokens; "
                                  f"{self.groups[gid].allocator.num_free} of {self.num_pages} are free")
         for gid, n in need.items():
-            rc.tables[gid].extend(self.groups[gid].allocator.allocate(n))
+            table = rc.tables[gid]
+            new = self.groups[gid].allocator.allocate(n)
+            if gid in self._table_updates:
+                self._table_updates[gid].extend((rc.slot, len(table) + i, p) for i, p in enumerate(new))
+            table.extend(new)
         rc.n_tokens = n_tokens
 
     def trim(self, rid: Hashable) -> int:
@@ -184,7 +198,29 @@ class CacheManager:
                     g.allocator.free([table[i]])
                     table[i] = -1
                     freed += 1
+                    if g.gid in self._table_updates:
+                        self._table_updates[g.gid].append((rc.slot, i, -1))
         return freed
+
+    def flush_table_updates(self) -> int:
+        """Bring the device-resident block tables up to date; returns the number
+        of entries written.  Rows of ended requests keep stale entries: a kernel
+        reads a row only up to its request's length, and the next owner of the
+        slot overwrites what it reads."""
+        import numpy as np
+        from ..ops import kernels as K
+        total = 0
+        for gid, ups in self._table_updates.items():
+            if not ups:
+                continue
+            arr = np.asarray([(s * self.table_width + i, p) for s, i, p in ups if i < self.table_width], dtype=np.int32)
+            self._table_updates[gid] = []
+            if arr.size == 0:
+                continue
+            dev = torch.from_numpy(np.ascontiguousarray(arr.T)).to(self.device, non_blocking=True)
+            K.scatter_i32(self.device_tables[gid], dev[0], dev[1])
+            total += arr.shape[0]
+        return total
 
     def release(self, rid: Hashable) -> None:
         """The request has ended: all its pages and its slot go back."""

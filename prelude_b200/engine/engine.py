@@ -23,8 +23,10 @@ import torch
 from ..cache.manager import CacheManager
 from ..config.registry import load_model_config
 from ..ops.library import require_device
-from ..sampling.sampler import Sampler
+from ..sampling.sampler import Sampler, sampling_mode
+from .graph import DecodeGraphs
 from .loading import load_model, parse_dtype
+from ..parts.model import DecoderModel
 from .runner import ModelRunner, StepEntry
 from .scheduler import CachePoolView, SamplingParams, Scheduler, SchedulerConfig
 
@@ -71,7 +73,8 @@ class Engine:
                  long_prefill_token_threshold: int = 0, max_total_tokens: int = 0, decode_reservation_cap: int = 0,
                  decode_priority_max_remaining_tokens: int = 4, cuda_graph: bool = True, cuda_graph_max_bs: int = 64,
                  max_model_len: Optional[int] = None):
-        """``model`` is a folder with config.json and safetensors files.
+        """``model`` is a folder with config.json and safetensors files (or a
+        DecoderModel that is already on the device).
 
         ``num_pages`` fixes the cache size; without it the cache takes what
         ``gpu_memory_utilization`` of the device leaves after the weights and a
@@ -82,8 +85,14 @@ class Engine:
         require_device()
         self.device = torch.device(device)
         self.dtype = parse_dtype(dtype)
-        self.config = load_model_config(model)
-        self.model = load_model(model, self.dtype, self.device)
+        if isinstance(model, DecoderModel):
+            # an already built model (random weights made on the device, toy architectures in tests)
+            self.config = None
+            self.model = model
+            self.device, self.dtype = model.ctx.device, model.ctx.dtype
+        else:
+            self.config = load_model_config(model)
+            self.model = load_model(model, self.dtype, self.device)
         spec = self.model.spec
         self.max_model_len = min(max_model_len or spec.max_positions, spec.max_positions)
         needs = self.model.cache_needs()
@@ -96,7 +105,8 @@ class Engine:
             num_pages = max(16, budget // per_page)
             # no more than every request slot at full length could use
             num_pages = min(num_pages, max_running_requests * -(-self.max_model_len // page_size))
-        self.cache = CacheManager(needs, page_size, int(num_pages), max_running_requests, self.device, self.dtype)
+        self.cache = CacheManager(needs, page_size, int(num_pages), max_running_requests, self.device, self.dtype,
+                                  max_request_tokens=self.max_model_len if cuda_graph else None)
         self.runner = ModelRunner(self.model, self.cache)
         self.sched_config = SchedulerConfig(
             max_running_requests=max_running_requests, max_num_batched_tokens=max_num_batched_tokens,
@@ -106,8 +116,7 @@ class Engine:
         self.sampler = Sampler(self.device)
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self.cuda_graph = cuda_graph
-        self.cuda_graph_max_bs = cuda_graph_max_bs
-        self._graphs = None
+        self.graphs = DecodeGraphs(self.runner, cuda_graph_max_bs) if cuda_graph else None
         self._stats = EngineStats(pages_total=int(num_pages))
         self._next_id = 0
 
@@ -201,16 +210,33 @@ class Engine:
             entries.append(StepEntry(it.seq.request_id, toks, [it.n_tokens - 1] if it.samples else []))
             if it.samples:
                 rows.append(it)
-        decode_only = all(it.n_tokens == 1 for it in items)
-        logits = self.runner.step(entries, check_status=False)
-        sampled = self.sampler.sample(
-            logits, [it.seq.params.temperature for it in rows], [it.seq.params.top_k for it in rows],
-            [it.seq.params.top_p for it in rows], [it.seq.params.seed for it in rows],
-            [len(it.seq.output) for it in rows]) if rows else []
-        code = int(self.runner.last_batch.status.item())
-        if code != 0:
-            raise RuntimeError(f"a kernel met a bad page id or position during the step (code {code})")
+        decode_only = all(it.n_tokens == 1 and it.samples for it in items)
+        temps = [it.seq.params.temperature for it in rows]
+        top_ks, top_ps = [it.seq.params.top_k for it in rows], [it.seq.params.top_p for it in rows]
+        seeds, counters = [it.seq.params.seed for it in rows], [len(it.seq.output) for it in rows]
         st = self._stats
+        if (decode_only and self.graphs is not None
+                and self.graphs.usable(len(items), max(it.start + 1 for it in items))):
+            # the captured step: same reservation, same kernels, fixed buffers
+            starts = self.runner.reserve(entries)
+            self.cache.flush_table_updates()
+            self.cache.zero_fresh_state()
+            g = self.graphs.get(len(items))
+            g.load([e.tokens[0] for e in entries], starts, [self.cache.slot_of(e.request_id) for e in entries],
+                   temps, seeds, counters)
+            g.replay()
+            sampled = g.fetch()
+            if any(sampling_mode(t, k, p) in ("top_p", "top_k_top_p") for t, k, p in zip(temps, top_ks, top_ps)):
+                sampled = self.sampler.sample(g.logits, temps, top_ks, top_ps, seeds, counters)
+            for e in entries:
+                self.cache.trim(e.request_id)
+            st.graph_steps += 1
+        else:
+            logits = self.runner.step(entries, check_status=False)
+            sampled = self.sampler.sample(logits, temps, top_ks, top_ps, seeds, counters) if rows else []
+            code = int(self.runner.last_batch.status.item())
+            if code != 0:
+                raise RuntimeError(f"a kernel met a bad page id or position during the step (code {code})")
         st.steps += 1
         st.decode_steps += 1 if decode_only else 0
         st.generated_tokens += len(rows)

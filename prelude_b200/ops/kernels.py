@@ -255,3 +255,26 @@ def softmax_temperature(logits: torch.Tensor, temperature: torch.Tensor) -> torc
 def philox_uniform(seed: int, counter: int) -> float:
     """The uniform number in [0, 1) the sampler draws for (seed, counter); host-side, for tests."""
     return float(_l.library().pb_philox_uniform(seed & (2**64 - 1), counter & (2**64 - 1)))
+
+
+def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """dst.view(-1)[idx[i]] = val[i] on the device (block-table updates before a captured step)."""
+    _need(dst, "dst", torch.int32)
+    _need(idx, "idx", torch.int32)
+    _need(val, "val", torch.int32)
+    if idx.numel() != val.numel():
+        raise KernelLibraryError("scatter_i32: one value per index")
+    check(_l.library().pb_scatter_i32(dst.data_ptr(), dst.numel(), idx.data_ptr(), val.data_ptr(), idx.numel(),
+                                      _ptr(status), _stream()), "scatter_i32")
+
+
+def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, counters: Optional[torch.Tensor],
+                   sampled: torch.Tensor, max_positions: int) -> None:
+    """tokens = sampled; positions += 1; counters += 1: a decode step that feeds itself."""
+    _need(tokens, "tokens", torch.int32)
+    _need(positions, "positions", torch.int32)
+    _need(sampled, "sampled", torch.int32)
+    if counters is not None:
+        _need(counters, "counters", torch.int64)
+    check(_l.library().pb_decode_advance(tokens.data_ptr(), positions.data_ptr(), _ptr(counters), sampled.data_ptr(),
+                                         tokens.numel(), int(max_positions), _stream()), "decode_advance")

@@ -38,6 +38,8 @@ _SIGNATURES = {
     "pb_sample": ([P, L, I, I, P, P, P, P, P], I),
     "pb_softmax_temperature": ([P, L, I, I, P, P, P], I),
     "pb_philox_uniform": ([c_uint64, c_uint64], F),
+    "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
+    "pb_decode_advance": ([P, P, P, P, I, I, P], I),
 }
 
 _lock = threading.Lock()
@@ -99,7 +101,12 @@ def last_error() -> str:
     return (library().pb_last_error() or b"").decode(errors="replace")
 
 
+launch_count = 0     # launcher calls so far in this process (a launcher issues one kernel)
+
+
 def check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if code != 0:
         raise KernelLibraryError(f"{what}: {last_error()}")
 
