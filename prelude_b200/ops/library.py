@@ -38,6 +38,9 @@ _SIGNATURES = {
     "pb_sample": ([P, L, I, I, P, P, P, P, P], I),
     "pb_softmax_temperature": ([P, L, I, I, P, P, P], I),
     "pb_philox_uniform": ([c_uint64, c_uint64], F),
+    "pb_attention_prefill_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P], I),
+    "pb_attention_decode_scratch_floats": ([I, I, I, I], L),
+    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
     "pb_decode_advance": ([P, P, P, P, I, I, P], I),
 }

@@ -308,3 +308,110 @@ def test_sampling_frequencies():
     freq = torch.bincount(got.long(), minlength=V).float() / n
     want = torch.softmax(logits[0] / 0.7, -1)
     assert (freq - want).abs().max() < 0.03
+
+
+# ---------------------------------------------------------------------------------------
+# tensor-core attention (bfloat16): prompt portions and decode steps, through the dispatch
+# ---------------------------------------------------------------------------------------
+def _batch_for(requests, page, num_pages, nKV, D, seed, trimmed_below=None):
+    """requests: list of (context_len, q_len): the last q_len tokens are this step's queries.
+    Returns (batch, k, v lists, pages, kp, vp)."""
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    kp = torch.full((num_pages, page, nKV, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vp = torch.full_like(kp, float("nan"))
+    ks, vs, tables, items = [], [], [], []
+    for i, (ctx, qn) in enumerate(requests):
+        k, v = rnd(ctx, nKV, D, dtype=torch.bfloat16, seed=seed + 10 * i + 1), rnd(ctx, nKV, D, dtype=torch.bfloat16, seed=seed + 10 * i + 2)
+        n = -(-ctx // page)
+        pages, perm = perm[:n], perm[n:]
+        for j in range(ctx):
+            kp[pages[j // page], j % page] = k[j]
+            vp[pages[j // page], j % page] = v[j]
+        if trimmed_below is not None:                       # pages wholly below this position have been given back
+            pages = [-1 if (pi + 1) * page <= trimmed_below[i] else pg for pi, pg in enumerate(pages)]
+        ks.append(k); vs.append(v); tables.append(pages)
+        items.append(StepItem(i, [0] * qn, ctx - qn))
+    batch = build_step_batch(items, {0: tables}, list(range(len(requests))), torch.device(DEV), 10, 1 << 20)
+    return batch, ks, vs, kp, vp
+
+
+def _check_dispatch(requests, nH, nKV, D, page, window, seed=0, trimmed_below=None, tolerance=None):
+    from prelude_b200.ops.attention import paged_attention
+    batch, ks, vs, kp, vp = _batch_for(requests, page, 600, nKV, D, seed, trimmed_below)
+    q = rnd(batch.n_tokens, nH, D, dtype=torch.bfloat16, seed=seed + 99)
+    got = paged_attention(q, kp, vp, batch, 0, 1 / math.sqrt(D), window)
+    assert int(batch.status.item()) == 0
+    row = 0
+    for i, (ctx, qn) in enumerate(requests):
+        want = _attention_plain(q[row:row + qn], ks[i], vs[i], list(range(ctx - qn, ctx)), 1 / math.sqrt(D), window)
+        diff = (got[row:row + qn].double() - want).abs().max()
+        assert diff <= (tolerance or tol(torch.bfloat16, 4.0)), (i, ctx, qn, float(diff))
+        row += qn
+    assert not torch.isnan(got.float()).any()
+    return got
+
+
+@pytest.mark.parametrize("nH,nKV,D,page", [(4, 2, 16, 4), (6, 2, 32, 8), (5, 1, 48, 16), (8, 8, 64, 16), (3, 3, 80, 16),
+                                           (32, 8, 128, 16), (2, 1, 256, 32), (16, 2, 128, 16), (7, 7, 112, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_prefill_tensor_cores(nH, nKV, D, page, window):
+    # whole prompts, a portion that continues a cached prefix, single tokens in between, a two-token portion
+    requests = [(83, 83), (200, 37), (150, 1), (2, 2), (130, 129), (65, 1), (64, 64)]
+    _check_dispatch(requests, nH, nKV, D, page, window)
+
+
+@pytest.mark.parametrize("nH,nKV,D,page", [(4, 2, 16, 4), (6, 2, 32, 8), (5, 1, 48, 16), (8, 8, 64, 16), (3, 3, 80, 16),
+                                           (32, 8, 128, 16), (2, 1, 256, 32), (16, 1, 128, 16), (7, 7, 112, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("splits", [None, 1, 3, 8])
+def test_attention_decode_tensor_cores(monkeypatch, nH, nKV, D, page, window, splits):
+    from prelude_b200.ops import attention
+    if splits is not None:
+        monkeypatch.setattr(attention, "decode_splits", lambda *a, **k: splits)
+    requests = [(1, 1), (2, 1), (63, 1), (64, 1), (65, 1), (128, 1), (129, 1), (500, 1), (777, 1)]
+    _check_dispatch(requests, nH, nKV, D, page, window)
+
+
+def test_attention_with_pages_that_a_window_has_given_back():
+    window = 40
+    reqs = [(300, 1), (170, 1)]
+    _check_dispatch(reqs, 8, 2, 64, 16, window, trimmed_below=[300 - window, 170 - window])
+    reqs = [(300, 30), (170, 2)]                       # portions: the first query still reads from ctx - q - window + 1
+    _check_dispatch(reqs, 8, 2, 64, 16, window, trimmed_below=[300 - 30 - window + 1, 170 - 2 - window + 1])
+
+
+@pytest.mark.parametrize("decode", [True, False])
+@pytest.mark.parametrize("where", ["far", "page_edge", "tile_edge", "window_first", "just_outside_window", "self"])
+def test_tensor_core_attention_finds_the_one_key_that_matters(monkeypatch, decode, where):
+    from prelude_b200.ops import attention
+    from prelude_b200.ops.attention import paged_attention
+    monkeypatch.setattr(attention, "decode_splits", lambda *a, **k: 5)
+    nH, nKV, D, page, L, window = 8, 2, 128, 16, 700, 200
+    qn = 1 if decode else 3
+    batch, ks, vs, kp, vp = _batch_for([(L, qn)], page, 64, nKV, D, seed=4)
+    pos = L - 1
+    target = {"far": 2, "page_edge": 15 * page, "tile_edge": 64 * 7 - 1, "window_first": pos - window + 1,
+              "just_outside_window": pos - window, "self": pos}[where]
+    unit = torch.zeros(D, device=DEV)
+    unit[9] = 1.0
+    q = rnd(qn, nH, D, dtype=torch.bfloat16, seed=5, scale=0.05)
+    q[-1] = (unit * 30).to(torch.bfloat16)
+    pg = int(batch.block_tables[0][0, target // page])
+    kp[:, :, :, :] = (kp.float() * 0.05).to(torch.bfloat16)
+    kp[pg, target % page] = (unit * 30).to(torch.bfloat16)         # score 900 / sqrt(128) = 80 against ~0
+    use_window = window if where in ("window_first", "just_outside_window") else None
+    got = paged_attention(q, kp, vp, batch, 0, 1 / math.sqrt(D), use_window)
+    hit = (got[-1, 0].float() - vs[0][target, 0].float()).abs().max() < 0.06
+    assert bool(hit) == (where != "just_outside_window")
+    ref = K().paged_attention_ref(q, kp, vp, batch.positions, batch.token_seq, batch.block_tables[0], 1 / math.sqrt(D), use_window)
+    assert (got.float() - ref.float()).abs().max() <= tol(torch.bfloat16, 4.0)
+
+
+def test_tensor_core_attention_refuses_or_falls_back():
+    from prelude_b200.ops.attention import tensor_core_shape_ok
+    assert tensor_core_shape_ok(32, 8, 128, True) and tensor_core_shape_ok(64, 1, 128, False)
+    assert not tensor_core_shape_ok(64, 1, 128, True) and not tensor_core_shape_ok(8, 8, 24, False)
+    _check_dispatch([(90, 1), (33, 1)], 40, 2, 64, 16, None)      # 20 heads per group: the plain kernel serves the decode step
+    _check_dispatch([(90, 5)], 8, 8, 24, 16, None)                # head size 24: plain kernel
