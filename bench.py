@@ -164,8 +164,10 @@ def time_decode(engine, cfg, batch, steps, warmup, seed):
     torch.cuda.synchronize()
     t0 = time.time()
     start.record()
+    torch.cuda.nvtx.range_push("timed_decode")          # lets a profiler pick these launches out
     for _ in range(steps):
         graph.replay()
+    torch.cuda.nvtx.range_pop()
     end.record()
     torch.cuda.synchronize()
     t1 = time.time()
@@ -193,7 +195,11 @@ def time_prefill(engine, cfg, warmup, reps=3):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         s.record()
+        if i >= warmup:
+            torch.cuda.nvtx.range_push("timed_prefill")
         runner.step([StepEntry(f"prefill{i}", ids, [PREFILL_TOKENS - 1])], check_status=False)
+        if i >= warmup:
+            torch.cuda.nvtx.range_pop()
         e.record()
         torch.cuda.synchronize()
         runner.finish(f"prefill{i}")

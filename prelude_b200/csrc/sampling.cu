@@ -10,12 +10,19 @@
 // step as counter, and the token is the first index whose cumulative
 // probability, summed in index order, exceeds u * total.
 //
-// One block per row.
+// Two passes.  The first cuts every row into chunks of a few thousand logits, one
+// block each: the chunk's maximum, its first index, and (when the row samples)
+// the chunk's sum of exp((x - chunk max) / T).  The second, one block per row,
+// combines the chunks in index order, and for a sampling row finds the chunk the
+// draw falls into and walks that chunk alone.
 #include "common.cuh"
 
 #include <math.h>
 
 #define SAMP_THREADS 1024
+#define PART_THREADS 256
+#define PART_CHUNK 4096
+#define PART_MAX_BLOCKS 64
 
 struct ArgPair {
     float v;
@@ -26,9 +33,10 @@ __device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
     return a;
 }
 
-__device__ ArgPair block_argmax(const float* __restrict__ row, int vocab, ArgPair* smem) {
+// Largest value and its first index over row[begin, end); every thread gets the result.
+__device__ ArgPair block_argmax(const float* __restrict__ row, int begin, int end, ArgPair* smem) {
     ArgPair best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         float v = row[i];
         if (v > best.v || (v == best.v && i < best.i)) best = ArgPair{v, i};   // NaN never wins
     }
@@ -43,24 +51,54 @@ __device__ ArgPair block_argmax(const float* __restrict__ row, int vocab, ArgPai
     ArgPair r = smem[0];
     for (int w = 1; w < nwarp; ++w) r = better(r, smem[w]);
     __syncthreads();
-    if (r.i == 0x7fffffff) r.i = 0;   // a row of NaN or -inf
     return r;
 }
 
-__global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, long long row_stride,
-                                                               int vocab, int32_t* __restrict__ out) {
-    __shared__ ArgPair smem[32];
-    ArgPair r = block_argmax(logits + (size_t)blockIdx.x * row_stride, vocab, smem);
-    if (threadIdx.x == 0) out[blockIdx.x] = r.i;
+__device__ float block_sum_ordered(float v, float* smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarp; ++w) total += smem[w];
+    __syncthreads();
+    return total;
 }
 
-PB_API int pb_argmax(const float* logits, long long row_stride, int rows, int vocab, int32_t* out,
-                     cudaStream_t stream) {
-    PB_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
-    if (rows == 0) return 0;
-    argmax_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, row_stride, vocab, out);
-    PB_CHECK_LAUNCH("argmax");
-    return 0;
+static int part_blocks(int vocab) {
+    int n = (vocab + PART_CHUNK - 1) / PART_CHUNK;
+    return n < 1 ? 1 : (n > PART_MAX_BLOCKS ? PART_MAX_BLOCKS : n);
+}
+
+// Floats of scratch that argmax and sample need for `rows` rows of `vocab` logits.
+PB_API long long pb_sample_scratch_floats(int rows, int vocab) { return (long long)rows * part_blocks(vocab) * 4; }
+
+// pass 1: grid (chunks, rows).  part[row][chunk] = {max, first index (int bits), sum of exp((x - max) / T), unused}
+__global__ void __launch_bounds__(PART_THREADS) sample_partial_kernel(
+    const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
+    float* __restrict__ part) {
+    __shared__ ArgPair smem[32];
+    __shared__ float red[32];
+    const int nblk = gridDim.x, b = blockIdx.x, r = blockIdx.y;
+    const int chunk = (vocab + nblk - 1) / nblk;
+    const int begin = min(vocab, b * chunk), end = min(vocab, begin + chunk);
+    const float* row = logits + (size_t)r * row_stride;
+    ArgPair top = block_argmax(row, begin, end, smem);
+    float sum = 0.f;
+    const float temp = temperature ? temperature[r] : 0.f;
+    if (temp >= 1e-7f && top.v > -INFINITY) {
+        const float inv_t = 1.0f / temp;
+        float local = 0.f;
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) local += expf((row[i] - top.v) * inv_t);
+        sum = block_sum_ordered(local, red);
+    }
+    if (threadIdx.x == 0) {
+        float* o = part + ((size_t)r * nblk + b) * 4;
+        o[0] = top.v;
+        o[1] = __int_as_float(top.i);
+        o[2] = sum;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -88,60 +126,109 @@ __host__ __device__ inline float philox_uniform(uint64_t seed, uint64_t counter)
 // For tests: the uniform number the sampler uses for (seed, counter).
 PB_API float pb_philox_uniform(uint64_t seed, uint64_t counter) { return philox_uniform(seed, counter); }
 
-__global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(
+// pass 2: one block per row
+__global__ void __launch_bounds__(PART_THREADS) sample_final_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
-    const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ counters, int32_t* __restrict__ out) {
-    __shared__ ArgPair smem[32];
-    __shared__ float sums[SAMP_THREADS];
-    __shared__ int winner;
-    const float* row = logits + (size_t)blockIdx.x * row_stride;
-    const float temp = temperature[blockIdx.x];
-    ArgPair top = block_argmax(row, vocab, smem);
-    if (!(temp >= 1e-7f)) {
-        if (threadIdx.x == 0) out[blockIdx.x] = top.i;
+    const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ counters, const float* __restrict__ part,
+    int nblk, int32_t* __restrict__ out) {
+    __shared__ float sums[PART_THREADS];
+    __shared__ float s_top, s_target;
+    __shared__ int s_chunk, s_best, s_winner;
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * row_stride;
+    const float* pr = part + (size_t)r * nblk * 4;
+    const float temp = temperature ? temperature[r] : 0.f;
+    const bool greedy = !(temp >= 1e-7f);
+    const float inv_t = greedy ? 0.f : 1.0f / temp;
+    if (threadIdx.x == 0) {
+        ArgPair best{-INFINITY, 0x7fffffff};
+        for (int b = 0; b < nblk; ++b) best = better(best, ArgPair{pr[4 * b], __float_as_int(pr[4 * b + 1])});
+        if (best.i == 0x7fffffff) best.i = 0;               // a row of NaN or -inf
+        s_best = best.i;
+        s_top = best.v;
+        s_chunk = -1;
+        s_winner = -1;
+        if (!greedy && best.v > -INFINITY) {
+            float total = 0.f;
+            for (int b = 0; b < nblk; ++b) total += pr[4 * b + 2] * expf((pr[4 * b] - best.v) * inv_t);
+            const float target = philox_uniform(seeds[r], counters[r]) * total;
+            float run = 0.f;
+            for (int b = 0; b < nblk; ++b) {
+                const float w = pr[4 * b + 2] * expf((pr[4 * b] - best.v) * inv_t);
+                if (target < run + w) { s_chunk = b; s_target = target - run; break; }
+                run += w;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_chunk < 0) {                                      // greedy, or rounding at the far end: the most likely token
+        if (threadIdx.x == 0) out[r] = s_best;
         return;
     }
-    const float inv_t = 1.0f / temp;
-    // contiguous chunk per thread, so that the cumulative sum runs in index order
-    const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
-    const int begin = min(vocab, (int)threadIdx.x * chunk), end = min(vocab, begin + chunk);
+    // walk the chunk that holds the draw: contiguous pieces per thread, cumulative sum in index order
+    const int chunk = (vocab + nblk - 1) / nblk;
+    const int cb = min(vocab, s_chunk * chunk), ce = min(vocab, cb + chunk);
+    const int piece = (ce - cb + blockDim.x - 1) / blockDim.x;
+    const int begin = min(ce, cb + (int)threadIdx.x * piece), end = min(ce, begin + piece);
+    const float top = s_top, target = s_target;
     float local = 0.f;
-    for (int i = begin; i < end; ++i) local += expf((row[i] - top.v) * inv_t);
+    for (int i = begin; i < end; ++i) local += expf((row[i] - top) * inv_t);
     sums[threadIdx.x] = local;
-    if (threadIdx.x == 0) winner = -1;
     __syncthreads();
-    // inclusive scan over the per-thread sums (Hillis-Steele)
-    for (int off = 1; off < blockDim.x; off <<= 1) {
+    for (int off = 1; off < blockDim.x; off <<= 1) {        // inclusive scan (Hillis-Steele)
         float add = threadIdx.x >= off ? sums[threadIdx.x - off] : 0.f;
         __syncthreads();
         sums[threadIdx.x] += add;
         __syncthreads();
     }
-    const float total = sums[blockDim.x - 1];
-    const float u = philox_uniform(seeds[blockIdx.x], counters[blockIdx.x]);
-    const float target = u * total;
-    const float incl = sums[threadIdx.x];
-    const float excl = threadIdx.x == 0 ? 0.f : sums[threadIdx.x - 1];
+    const float incl = sums[threadIdx.x], excl = threadIdx.x == 0 ? 0.f : sums[threadIdx.x - 1];
     if (begin < end && excl <= target && target < incl) {
-        // this thread's chunk holds the draw: walk it
         float run = excl;
         int pick = end - 1;
         for (int i = begin; i < end; ++i) {
-            run += expf((row[i] - top.v) * inv_t);
+            run += expf((row[i] - top) * inv_t);
             if (target < run) { pick = i; break; }
         }
-        atomicMax(&winner, pick);   // exactly one thread satisfies the test
+        atomicMax(&s_winner, pick);                         // at most one thread satisfies the test
     }
     __syncthreads();
-    if (threadIdx.x == 0) out[blockIdx.x] = winner >= 0 ? winner : top.i;   // rounding at the far end: most likely token
+    if (threadIdx.x == 0) {
+        int w = s_winner;
+        if (w < 0) {                                        // the chunk total and the walk disagree in the last bit: last token with weight
+            w = ce - 1;
+        }
+        out[r] = w;
+    }
+}
+
+static int launch_two_pass(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
+                           const uint64_t* seeds, const uint64_t* counters, float* scratch, int32_t* out,
+                           cudaStream_t stream) {
+    const int nblk = part_blocks(vocab);
+    sample_partial_kernel<<<dim3(nblk, rows), PART_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, scratch);
+    sample_final_kernel<<<rows, PART_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, seeds, counters,
+                                                           scratch, nblk, out);
+    return 0;
+}
+
+// scratch: pb_sample_scratch_floats(rows, vocab) floats.
+PB_API int pb_argmax(const float* logits, long long row_stride, int rows, int vocab, int32_t* out, float* scratch,
+                     cudaStream_t stream) {
+    PB_REQUIRE(rows >= 0 && rows < 65536 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
+    PB_REQUIRE(logits && out && scratch, "argmax: null pointer");
+    if (rows == 0) return 0;
+    launch_two_pass(logits, row_stride, rows, vocab, nullptr, nullptr, nullptr, scratch, out, stream);
+    PB_CHECK_LAUNCH("argmax");
+    return 0;
 }
 
 PB_API int pb_sample(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
-                     const uint64_t* seeds, const uint64_t* counters, int32_t* out, cudaStream_t stream) {
-    PB_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
-    PB_REQUIRE(logits && temperature && seeds && counters && out, "sample: null pointer");
+                     const uint64_t* seeds, const uint64_t* counters, int32_t* out, float* scratch,
+                     cudaStream_t stream) {
+    PB_REQUIRE(rows >= 0 && rows < 65536 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    PB_REQUIRE(logits && temperature && seeds && counters && out && scratch, "sample: null pointer");
     if (rows == 0) return 0;
-    sample_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, seeds, counters, out);
+    launch_two_pass(logits, row_stride, rows, vocab, temperature, seeds, counters, scratch, out, stream);
     PB_CHECK_LAUNCH("sample");
     return 0;
 }
@@ -154,7 +241,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) softmax_temperature_kernel(
     __shared__ float red[32];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     float* prow = probs + (size_t)blockIdx.x * vocab;
-    ArgPair top = block_argmax(row, vocab, smem);
+    ArgPair top = block_argmax(row, 0, vocab, smem);
     const float inv_t = 1.0f / fmaxf(temperature[blockIdx.x], 1e-7f);
     float local = 0.f;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {

@@ -29,13 +29,25 @@ def _sm_count(device) -> int:
     return SM_COUNT
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, max_context: int, device) -> int:
+_counters = {}
+
+
+def _decode_counters(device) -> torch.Tensor:
+    """Arrival counters of the split decode kernel: zero before the first call,
+    left at zero by every call, so one buffer serves all calls on a stream."""
+    buf = _counters.get(device)
+    if buf is None:
+        buf = _counters[device] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return buf
+
+
+def decode_splits(n_tokens: int, n_kv_heads: int, head_dim: int, max_context: int, device) -> int:
     """Over how many blocks a decode step spreads the keys of one (token, key/value head):
-    enough that the grid fills the device about twice, never more than there are 64-key tiles."""
+    as many as the device holds at one time, never more than there are 64-key tiles."""
+    resident = _sm_count(device) * _l.library().pb_attention_decode_blocks_per_sm(head_dim)
     blocks = max(1, n_tokens * n_kv_heads)
-    want = -(-2 * _sm_count(device) // blocks)
     tiles = max(1, -(-max_context // 64))
-    return max(1, min(want, tiles, 64))
+    return max(1, min(resident // blocks, tiles, 64))
 
 
 def _prefill_plan(batch, group: int):
@@ -81,13 +93,17 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         max_ctx = batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size
         if window:
             max_ctx = min(max_ctx, window + 64)
-        splits = decode_splits(T, nKV, max_ctx, q.device)
+        splits = decode_splits(T, nKV, D, max_ctx, q.device)
+        if T * nKV > (1 << 16):
+            splits = 1
         n = lib.pb_attention_decode_scratch_floats(T, nH, D, splits)
         scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
+        counters = _decode_counters(q.device) if n else None
         check(lib.pb_attention_decode_bf16(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
             batch.positions.data_ptr(), batch.token_seq.data_ptr(), page_size, num_pages, T, nH, nKV, D, float(scale),
-            win, splits, None if scratch is None else scratch.data_ptr(), batch.status.data_ptr(), stream),
+            win, splits, None if scratch is None else scratch.data_ptr(),
+            None if counters is None else counters.data_ptr(), batch.status.data_ptr(), stream),
             "attention_decode")
         return out
     tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, nH // nKV)

@@ -223,7 +223,10 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
         raise KernelLibraryError("argmax: logits must be [rows, vocab] with dense rows")
     rows, vocab = logits.shape
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    check(_l.library().pb_argmax(logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    lib = _l.library()
+    scratch = torch.empty(max(1, lib.pb_sample_scratch_floats(rows, vocab)), dtype=torch.float32, device=logits.device)
+    check(lib.pb_argmax(logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), scratch.data_ptr(), _stream()),
+          "argmax")
     return out
 
 
@@ -237,8 +240,10 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor,
     if not (temperature.numel() == seeds.numel() == counters.numel() == rows):
         raise KernelLibraryError("sample: one temperature, seed and counter per row")
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    check(_l.library().pb_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
-                                 seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _stream()), "sample")
+    lib = _l.library()
+    scratch = torch.empty(max(1, lib.pb_sample_scratch_floats(rows, vocab)), dtype=torch.float32, device=logits.device)
+    check(lib.pb_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(), seeds.data_ptr(),
+                        counters.data_ptr(), out.data_ptr(), scratch.data_ptr(), _stream()), "sample")
     return out
 
 

@@ -34,13 +34,18 @@ _SIGNATURES = {
     "pb_paged_attention_ref": ([P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P], I),
     "pb_silu_mul": ([P, P, I, I, I, P], I),
     "pb_gemm_ref": ([P, P, P, P, I, I, I, I, I, L, L, L, P], I),
-    "pb_argmax": ([P, L, I, I, P, P], I),
-    "pb_sample": ([P, L, I, I, P, P, P, P, P], I),
+    "pb_sample_scratch_floats": ([I, I], L),
+    "pb_argmax": ([P, L, I, I, P, P, P], I),
+    "pb_sample": ([P, L, I, I, P, P, P, P, P, P], I),
     "pb_softmax_temperature": ([P, L, I, I, P, P, P], I),
     "pb_philox_uniform": ([c_uint64, c_uint64], F),
     "pb_attention_prefill_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P], I),
     "pb_attention_decode_scratch_floats": ([I, I, I, I], L),
-    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P], I),
+    "pb_attention_decode_blocks_per_sm": ([I], I),
+    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P], I),
+    "pb_gemm_skinny_scratch_bytes": ([I, I, I], L),
+    "pb_gemm_skinny_supported": ([I, I, I, L, L], I),
+    "pb_gemm_skinny_bf16": ([P, P, P, P, I, I, I, L, L, L, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
     "pb_decode_advance": ([P, P, P, P, I, I, P], I),
 }

@@ -415,3 +415,38 @@ def test_tensor_core_attention_refuses_or_falls_back():
     assert not tensor_core_shape_ok(64, 1, 128, True) and not tensor_core_shape_ok(8, 8, 24, False)
     _check_dispatch([(90, 1), (33, 1)], 40, 2, 64, 16, None)      # 20 heads per group: the plain kernel serves the decode step
     _check_dispatch([(90, 5)], 8, 8, 24, 16, None)                # head size 24: plain kernel
+
+
+# ---------------------------------------------------------------------------------------
+# the weight-streaming product for decode steps
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K_", [(2560, 4096), (19456, 2560), (6144, 2560), (2560, 9728), (48, 64), (16, 32),
+                                  (176, 96), (1008, 1504)])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+def test_gemm_skinny(M, N, K_):
+    from prelude_b200.ops.linear import gemm_skinny
+    x, w, b = rnd(M, K_, dtype=torch.bfloat16, seed=21), rnd(N, K_, dtype=torch.bfloat16, seed=22, scale=0.05), rnd(N, seed=23)
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    got = gemm_skinny(x, w)
+    assert (got.double() - want).abs().max() <= tol(torch.bfloat16, scale)
+    assert torch.equal(gemm_skinny(x, w), got)                       # counters are back at zero, same sums
+    got_b = gemm_skinny(x, w, b)
+    assert (got_b.double() - (want + b.double())).abs().max() <= tol(torch.bfloat16, float((want + b.double()).abs().max()))
+    if M > 1:                                                        # a row does not depend on the rest of the batch
+        assert torch.equal(gemm_skinny(x[M - 1:M].contiguous(), w), got[M - 1:M])
+    wide = rnd(M, K_ + 64, dtype=torch.bfloat16, seed=24)            # x as a view into a wider tensor
+    assert torch.equal(gemm_skinny(wide[:, 32:32 + K_], w), gemm_skinny(wide[:, 32:32 + K_].contiguous(), w))
+
+
+def test_gemm_skinny_refuses_other_shapes_and_linear_falls_back():
+    from prelude_b200.ops.library import KernelLibraryError
+    from prelude_b200.ops.linear import gemm_skinny, linear, skinny_takes
+    x, w = rnd(4, 72, dtype=torch.bfloat16), rnd(40, 72, dtype=torch.bfloat16)
+    assert not skinny_takes(x, w)
+    with pytest.raises(KernelLibraryError, match="not taken"):
+        gemm_skinny(x, w)
+    want = x.double() @ w.double().T
+    assert (linear(x, w).double() - want).abs().max() <= tol(torch.bfloat16, float(want.abs().max()))
+    assert not skinny_takes(rnd(100, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
+    assert skinny_takes(rnd(8, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
