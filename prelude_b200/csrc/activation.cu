@@ -7,6 +7,8 @@
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n_tokens, int inter) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long total = n_tokens * inter;
     if (idx >= total) return;
@@ -20,6 +22,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
 // bfloat16, 8 elements per thread; inter % 8 == 0.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                        long long n_tokens, int inter) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int per_row = inter / 8;
     if (idx >= n_tokens * per_row) return;
@@ -45,13 +49,13 @@ PB_API int pb_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, 
     const int threads = 256;
     if (dtype == PB_BF16 && inter % 8 == 0 && pb_aligned(gate_up, 16) && pb_aligned(out, 16)) {
         long long n = (long long)n_tokens * (inter / 8);
-        silu_mul_bf16x8_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, stream>>>(
+        pb_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n_tokens, inter);
     } else {
         long long n = (long long)n_tokens * inter;
         PB_REQUIRE((n + threads - 1) / threads < (1ll << 31), "silu_mul: too many elements");
         PB_DISPATCH_DTYPE(dtype, T,
-            (silu_mul_kernel<T><<<(unsigned)((n + threads - 1) / threads), threads, 0, stream>>>(
+            (pb_launch(silu_mul_kernel<T>, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream, 
                 (const T*)gate_up, (T*)out, n_tokens, inter)));
     }
     PB_CHECK_LAUNCH("silu_mul");

@@ -41,6 +41,7 @@ struct DecodeParams {
 
 template <int DMAX>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams dp) {
+    pb_grid_dep_launch();
     const AttnParams& p = dp.a;
     constexpr int STRIDE = DMAX + 8;
     constexpr int KSTEPS = DMAX / 16;
@@ -81,6 +82,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
         const bool pages_in_smem = n_pages <= DEC_MAX_PAGES;
         if (pages_in_smem)
             for (int i = threadIdx.x; i < n_pages; i += ATT_THREADS) s_pages[i] = table[page_first + i];
+        // positions and block tables were written before the previous kernel started; q and the
+        // newest keys and values are that kernel's output
+        pb_grid_dep_wait();
         // q rows of the group (rows from G on are zero)
         const int chunks = d >> 3;
         for (int c = threadIdx.x; c < 16 * chunks; c += ATT_THREADS) {
@@ -212,6 +216,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
             __syncthreads();
         }
     }
+    pb_grid_dep_wait();                                     // blocks without keys come here directly
     // merge the four warps through shared memory (the tile buffers are free now)
     float* sO = reinterpret_cast<float*>(sKV);              // [4][16][DMAX]
     float* sM = sO + 4 * 16 * DMAX;                         // [4][16]
@@ -299,7 +304,7 @@ static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
         if (e != cudaSuccess) return pb_fail("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_decode_kernel<DMAX><<<dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), ATT_THREADS, smem, stream>>>(dp);
+    pb_launch(attn_decode_kernel<DMAX>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(ATT_THREADS), smem, stream, dp);
     return 0;
 }
 

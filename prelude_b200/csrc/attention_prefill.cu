@@ -34,6 +34,8 @@
 // ---------------------------------------------------------------------------------------
 template <int DMAX>
 __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnParams p) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     constexpr int STRIDE = DMAX + 8;
     constexpr int KSTEPS = DMAX / 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -199,7 +201,7 @@ static int launch_prefill(const AttnParams& p, int n_tiles, cudaStream_t stream)
         if (e != cudaSuccess) return pb_fail("attention_prefill: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_prefill_kernel<DMAX><<<dim3(n_tiles, p.n_kv_heads), ATT_THREADS, smem, stream>>>(p);
+    pb_launch(attn_prefill_kernel<DMAX>, dim3(n_tiles, p.n_kv_heads), dim3(ATT_THREADS), smem, stream, p);
     return 0;
 }
 

@@ -27,6 +27,8 @@ __global__ void paged_attention_warp_kernel(
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages, int n_tokens,
     int n_heads, int n_kv_heads, int head_dim, float scale, int window, int* __restrict__ status) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float q_s[ATTN_REF_WARPS][ATTN_REF_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * ATTN_REF_WARPS + warp;
@@ -114,7 +116,7 @@ PB_API int pb_paged_attention_ref(const void* q, const void* k_pages, const void
     long long blocks = (items + ATTN_REF_WARPS - 1) / ATTN_REF_WARPS;
     PB_REQUIRE(blocks < (1ll << 31), "paged_attention_ref: too many rows");
     PB_DISPATCH_DTYPE(dtype, T,
-        (paged_attention_warp_kernel<T><<<(unsigned)blocks, ATTN_REF_WARPS * 32, 0, stream>>>(
+        (pb_launch(paged_attention_warp_kernel<T>, dim3((unsigned)blocks), dim3(ATTN_REF_WARPS * 32), 0, stream, 
             (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, positions, token_seq, block_table,
             table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, status)));
     PB_CHECK_LAUNCH("paged_attention_ref");

@@ -2,6 +2,7 @@
 #include "common.cuh"
 
 #include <stdarg.h>
+#include <stdlib.h>
 
 static thread_local char g_pb_error[1024] = "";
 
@@ -11,6 +12,15 @@ int pb_fail(const char* fmt, ...) {
     vsnprintf(g_pb_error, sizeof(g_pb_error), fmt, ap);
     va_end(ap);
     return 1;
+}
+
+bool pb_pdl_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char* off = getenv("PRELUDE_NO_PDL");
+        state = (off && off[0] && off[0] != '0') ? 0 : 1;
+    }
+    return state == 1;
 }
 
 // Message of the last failed call on this thread.

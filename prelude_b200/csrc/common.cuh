@@ -52,6 +52,39 @@ __device__ __forceinline__ float pb_warp_max(float v) {
     return v;
 }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Kernels of this library are launched with
+// the attribute that lets the next kernel on the stream start while this one is
+// still running.  Every kernel calls pb_grid_dep_launch() as early as it can
+// (its dependents may then be placed on free multiprocessors) and
+// pb_grid_dep_wait() before it first touches memory that the kernel before it
+// on the stream may write or read; the wait returns when that kernel has
+// finished and its writes are visible.  What runs before the wait - index
+// arithmetic, barrier set-up, reads of data that older kernels produced -
+// overlaps the tail of the previous kernel.  A kernel launched without the
+// attribute passes both calls at once.  PRELUDE_NO_PDL=1 turns the attribute off.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pb_grid_dep_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pb_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+bool pb_pdl_enabled();   // common.cu
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t pb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pb_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Dispatch a launcher body on an element type code.
 #define PB_DISPATCH_DTYPE(code, T, ...)                              \
     do {                                                             \

@@ -8,6 +8,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                     float* __restrict__ out, int n_tokens, int width, int vocab) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     int t = blockIdx.x;
     if (t >= n_tokens) return;
     int id = ids[t];
@@ -23,6 +25,8 @@ __global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const T* __
 // bfloat16 rows, 8 elements per thread and access; needs width % 8 == 0.
 __global__ void embed_gather_bf16x8_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                            float* __restrict__ out, int n_tokens, int width, int vocab) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     int t = blockIdx.x;
     if (t >= n_tokens) return;
     int id = ids[t];
@@ -45,11 +49,11 @@ PB_API int pb_embed_gather(const int32_t* ids, const void* table, int table_dtyp
     if (n_tokens == 0) return 0;
     int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == PB_BF16 && width % 8 == 0 && pb_aligned(table, 16) && pb_aligned(out, 16)) {
-        embed_gather_bf16x8_kernel<<<n_tokens, threads, 0, stream>>>(
+        pb_launch(embed_gather_bf16x8_kernel, dim3(n_tokens), dim3(threads), 0, stream, 
             ids, (const __nv_bfloat16*)table, out, n_tokens, width, vocab);
     } else {
         PB_DISPATCH_DTYPE(table_dtype, T,
-            (embed_gather_kernel<T><<<n_tokens, threads, 0, stream>>>(ids, (const T*)table, out, n_tokens, width, vocab)));
+            (pb_launch(embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const T*)table, out, n_tokens, width, vocab)));
     }
     PB_CHECK_LAUNCH("embed_gather");
     return 0;

@@ -19,6 +19,8 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256) gemm_ref_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                        const float* __restrict__ bias, TC* __restrict__ C, int M,
                                                        int N, int K, long long lda, long long ldw, long long ldc) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float As[GR_BK][GR_BM + 1];
     __shared__ float Ws[GR_BK][GR_BN + 1];
     const int tid = threadIdx.x;
@@ -81,13 +83,13 @@ PB_API int pb_gemm_ref(const void* A, const void* W, const float* bias, void* C,
     dim3 grid((N + GR_BN - 1) / GR_BN, (M + GR_BM - 1) / GR_BM);
     PB_REQUIRE(grid.y < 65536, "gemm_ref: M=%d too large", M);
     if (in_dtype == PB_F32 && out_dtype == PB_F32)
-        gemm_ref_kernel<float, float, float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, bias,
+        pb_launch(gemm_ref_kernel<float, float, float>, dim3(grid), dim3(256), 0, stream, (const float*)A, (const float*)W, bias,
                                                                       (float*)C, M, N, K, lda, ldw, ldc);
     else if (in_dtype == PB_BF16 && out_dtype == PB_BF16)
-        gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+        pb_launch(gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 
             (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc);
     else if (in_dtype == PB_BF16 && out_dtype == PB_F32)
-        gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, float><<<grid, 256, 0, stream>>>(
+        pb_launch(gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, stream, 
             (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
     else
         return pb_fail("gemm_ref: unsupported types in=%d out=%d", in_dtype, out_dtype);

@@ -61,6 +61,8 @@ struct SkinnyParams {
 // MT: number of 8-row tiles of x (M <= 8 * MT)
 template <int MT>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyParams p) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     constexpr int MP = 8 * MT;
     __shared__ float red[SK_KW][SK_ROWS][MP + 1];
     __shared__ int s_last;
@@ -221,10 +223,10 @@ PB_API int pb_gemm_skinny_bf16(const void* X, const void* W, const float* bias, 
     const int mp = M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64;
     p.counters = (int*)scratch;
     p.scratch = (float*)((char*)scratch + (size_t)SK_MAX_GROUPS * 4);
-    if (mp == 8) gemm_skinny_kernel<1><<<blocks, SK_THREADS, 0, stream>>>(p);
-    else if (mp == 16) gemm_skinny_kernel<2><<<blocks, SK_THREADS, 0, stream>>>(p);
-    else if (mp == 32) gemm_skinny_kernel<4><<<blocks, SK_THREADS, 0, stream>>>(p);
-    else gemm_skinny_kernel<8><<<blocks, SK_THREADS, 0, stream>>>(p);
+    if (mp == 8) pb_launch(gemm_skinny_kernel<1>, dim3(blocks), dim3(SK_THREADS), 0, stream, p);
+    else if (mp == 16) pb_launch(gemm_skinny_kernel<2>, dim3(blocks), dim3(SK_THREADS), 0, stream, p);
+    else if (mp == 32) pb_launch(gemm_skinny_kernel<4>, dim3(blocks), dim3(SK_THREADS), 0, stream, p);
+    else pb_launch(gemm_skinny_kernel<8>, dim3(blocks), dim3(SK_THREADS), 0, stream, p);
     PB_CHECK_LAUNCH("gemm_skinny");
     return 0;
 }

@@ -1,0 +1,466 @@
+// C = A * B^T on the fifth-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands brought to shared memory by TMA.
+//
+//   A: [rows_a, K] bfloat16, K contiguous     B: [rows_b, K] bfloat16, K contiguous
+//   C[i, j] = sum_k A[i, k] * B[j, k]          float32 accumulation
+//
+// One kernel serves both shapes of a linear layer y = x W^T:
+//   * many tokens (prompt portions):  A = x (128 tokens per tile), B = W (256
+//     features per tile), y[i, j] = C[i, j];
+//   * few tokens (decode steps):      A = W (128 features per tile), B = x (the
+//     batch padded to 16, 32 or 64), y[j, i] = C[i, j] - the weight matrix is the
+//     128-row operand, so every weight byte is read once and the tensor cores'
+//     row dimension is full whatever the batch size.
+// (The reference sends these products to DeepGEMM / CUTLASS / cuBLAS,
+// crates/prelude-cuda/src/ops/gemm.rs:35-137; its sm_100 path is
+// crates/prelude-cuda/deepgemm/src/sm100_bf16.cuh:10-205.)
+//
+// Structure.  A persistent grid, one block per multiprocessor.  The work is the
+// list of (output tile, 64-wide k block) items in tile-major order; every block
+// takes one contiguous run of items, so all blocks move the same number of bytes
+// whatever the shape.  A run of items inside one tile is a segment: its products
+// are accumulated in tensor memory.  A segment that covers its tile's whole K is
+// written straight to the output; otherwise the block writes a float32 partial
+// tile to scratch memory and counts itself in, and the block that arrives last
+// for the tile adds the partial tiles up in block order and writes the output
+// (the counters are left at zero for the next call).
+//
+// Warps: 0..3 read accumulators out of tensor memory and store (tcgen05.ld; warp w
+// owns lanes 32w..32w+31), warp 4 issues the TMA loads (one lane), warp 5 owns the
+// tensor memory allocation and issues the MMAs (one lane).  Shared memory is a
+// ring of stages (A tile 128 x 64, B tile BN x 64, 128-byte swizzle) with a full
+// and an empty barrier each; tensor memory holds two accumulators so that a
+// segment's stores overlap the next segment's products.  Every wait on a barrier
+// is bounded in time; a block that gives up raises the status word, frees its
+// tensor memory and returns.  No load uses cluster multicast.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <stdlib.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// about a second at most; false on giving up
+__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, unsigned parity) {
+    if (tc_mbar_try(bar, parity)) return true;
+    const long long start = clock64();
+    while (clock64() - start < (1ll << 31)) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (tc_mbar_try(bar, parity)) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tc_tma_load_2d(void* smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(tc_smem(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_tmem_alloc(uint32_t* holder, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(holder)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_tmem_dealloc(uint32_t taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the barrier gets one arrival when all MMAs issued so far by this thread have finished
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem(bar)) : "memory");
+}
+// 16 consecutive float32 columns of this thread's lane
+__device__ __forceinline__ void tc_tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_bar_epilogue() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle
+// (what TMA writes for a {64 x rows} bfloat16 box): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t tc_smem_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((tc_smem(tile) & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                                    // leading dimension byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                          // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                                    // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                                    // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = bn.
+__device__ __forceinline__ uint32_t tc_instr_desc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+struct TcParams {
+    void* out;                  // bfloat16 or float32
+    const float* bias;          // per feature, or null
+    float* scratch;             // [grid][2][128][BN] partial tiles
+    int* counters;              // [tiles], zero on entry and on exit
+    int* status;
+    long long ldo;
+    int rows_a, rows_b, K;
+    int tiles_a, tiles_b, kblocks, items_per_block;
+    int transposed;             // 1: out[j, i] = C[i, j] (A holds the weights); 0: out[i, j] = C[i, j]
+    int out_f32;
+};
+
+template <int BN>
+struct TcShared {
+    static constexpr int STAGE_BYTES = TC_A_BYTES + BN * TC_BK * 2;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 10 ? 10 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+    pb_grid_dep_launch();
+    using S = TcShared<BN>;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ int s_flag, s_ok;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int items_total = p.tiles_a * p.tiles_b * p.kblocks;
+    const int my_begin = blockIdx.x * p.items_per_block;
+    const int my_end = min(items_total, my_begin + p.items_per_block);
+
+    if (threadIdx.x == 0) {
+        s_ok = 1;
+        for (int s = 0; s < S::STAGES; ++s) { tc_mbar_init(&full_bar[s], 1); tc_mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { tc_mbar_init(&acc_full[a], 1); tc_mbar_init(&acc_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 5) tc_tmem_alloc(&tmem_holder, S::TMEM_COLS);
+    if (warp == 4 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_holder;
+    // barriers, tensor memory and descriptors are set up; from here on the operands are read
+    pb_grid_dep_wait();
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int fill = 0;
+            bool ok = true;
+            for (int it = my_begin; it < my_end && ok; ++it, ++fill) {
+                const int tile = it / p.kblocks, kb = it - tile * p.kblocks;
+                const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;      // A tiles vary fastest: neighbours share the B panel
+                const int stage = fill % S::STAGES;
+                ok = tc_mbar_wait(&empty_bar[stage], ((fill / S::STAGES) & 1) ^ 1);
+                if (!ok) break;
+                unsigned char* sa = smem + stage * S::STAGE_BYTES;
+                tc_mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+                tc_tma_load_2d(sa, &map_a, kb * TC_BK, ta * TC_BM, &full_bar[stage]);
+                tc_tma_load_2d(sa + TC_A_BYTES, &map_b, kb * TC_BK, tb * BN, &full_bar[stage]);
+            }
+            if (!ok && p.status) atomicExch(p.status, 8);
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = tc_instr_desc(BN);
+            int fill = 0, seg = 0;
+            bool ok = true;
+            for (int it = my_begin; it < my_end && ok; ++seg) {
+                const int tile = it / p.kblocks;
+                const int seg_end = min(my_end, (tile + 1) * p.kblocks);
+                const int acc = seg & 1;
+                ok = tc_mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int i = it; i < seg_end; ++i, ++fill) {
+                    const int stage = fill % S::STAGES;
+                    ok = tc_mbar_wait(&full_bar[stage], (fill / S::STAGES) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const unsigned char* sa = smem + stage * S::STAGE_BYTES;
+                    const uint64_t da = tc_smem_desc(sa), db = tc_smem_desc(sa + TC_A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)                         // 32 bytes along K per instruction
+                        tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (i > it || k > 0) ? 1u : 0u);
+                    tc_commit(&empty_bar[stage]);                                // the stage is free when these finish
+                }
+                if (!ok) break;
+                tc_commit(&acc_full[acc]);
+                it = seg_end;
+            }
+            if (!ok && p.status) atomicExch(p.status, 9);
+        }
+    } else {
+        // ---------------- epilogue: 4 warps, 128 accumulator rows ----------------
+        const int row = warp * 32 + lane;                                        // row of the tile = tensor-memory lane
+        int seg = 0;
+        bool ok = true;
+        for (int it = my_begin; it < my_end; ++seg) {
+            const int tile = it / p.kblocks;
+            const int tile_begin = tile * p.kblocks, tile_end = tile_begin + p.kblocks;
+            const int seg_end = min(my_end, tile_end);
+            const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+            const int acc = seg & 1;
+            if (ok) ok = tc_mbar_wait(&acc_full[acc], (seg >> 1) & 1);
+            if (!ok) s_ok = 0;
+            tc_bar_epilogue();                                                   // the four warps go on, or give up, together
+            if (!s_ok) { ok = false; break; }
+            tc_fence_after();
+            const bool whole = (it == tile_begin) && (seg_end == tile_end);
+            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(warp * 32) << 16);
+            const int gi = ta * TC_BM + row;                                     // row of A
+            float* part = p.scratch + ((size_t)blockIdx.x * 2 + (it == my_begin ? 0 : 1)) * TC_BM * BN + (size_t)row * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tc_tmem_ld16(taddr + c0, v);
+                if (!whole) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        *reinterpret_cast<float4*>(part + c0 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else if (gi >= p.rows_a) {
+                    // a row beyond the matrix: nothing to store
+                } else if (p.transposed) {
+                    const float b = p.bias ? p.bias[gi] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int gj = tb * BN + c0 + j;
+                        if (gj < p.rows_b) {
+                            if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)gj * p.ldo + gi] = v[j] + b;
+                            else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)gj * p.ldo + gi] = __float2bfloat16_rn(v[j] + b);
+                        }
+                    }
+                } else {
+                    const int gj0 = tb * BN + c0;
+                    if (p.out_f32) {
+                        float* o = reinterpret_cast<float*>(p.out) + (size_t)gi * p.ldo + gj0;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (gj0 + j < p.rows_b) o[j] = v[j] + (p.bias ? p.bias[gj0 + j] : 0.f);
+                    } else {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)gi * p.ldo + gj0;
+                        if (gj0 + 16 <= p.rows_b && !p.bias && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                            uint4 w0, w1;
+                            __nv_bfloat162 h[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            w0 = make_uint4(*(unsigned*)&h[0], *(unsigned*)&h[1], *(unsigned*)&h[2], *(unsigned*)&h[3]);
+                            w1 = make_uint4(*(unsigned*)&h[4], *(unsigned*)&h[5], *(unsigned*)&h[6], *(unsigned*)&h[7]);
+                            reinterpret_cast<uint4*>(o)[0] = w0;
+                            reinterpret_cast<uint4*>(o)[1] = w1;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (gj0 + j < p.rows_b) o[j] = __float2bfloat16_rn(v[j] + (p.bias ? p.bias[gj0 + j] : 0.f));
+                        }
+                    }
+                }
+                __syncwarp();                                                    // the next tensor-memory load needs the whole warp
+            }
+            // the accumulator may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&acc_empty[acc]);
+            if (!whole) {
+                // count this block in; the last one for the tile adds the partial tiles up, in block order
+                const int c_first = tile_begin / p.items_per_block, c_last = (tile_end - 1) / p.items_per_block;
+                __threadfence();
+                tc_bar_epilogue();
+                if (threadIdx.x == 0) {
+                    const int old = atomicAdd(p.counters + tile, 1);
+                    s_flag = (old == c_last - c_first);
+                    if (s_flag) p.counters[tile] = 0;
+                }
+                tc_bar_epilogue();
+                if (s_flag) {
+                    __threadfence();
+                    for (int c0 = 0; c0 < BN; c0 += 4) {
+                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int c = c_first; c <= c_last; ++c) {
+                            const int slot = (max(c * p.items_per_block, tile_begin) == c * p.items_per_block) ? 0 : 1;
+                            const float4 x = __ldcg(reinterpret_cast<const float4*>(
+                                p.scratch + ((size_t)c * 2 + slot) * TC_BM * BN + (size_t)row * BN + c0));
+                            sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+                        }
+                        if (gi >= p.rows_a) continue;
+                        const float vv[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int gj = tb * BN + c0 + j;
+                            if (gj >= p.rows_b) continue;
+                            const float b = p.bias ? p.bias[p.transposed ? gi : gj] : 0.f;
+                            const size_t at = p.transposed ? ((size_t)gj * p.ldo + gi) : ((size_t)gi * p.ldo + gj);
+                            if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = vv[j] + b;
+                            else reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(vv[j] + b);
+                        }
+                    }
+                }
+                tc_bar_epilogue();
+            }
+            it = seg_end;
+        }
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 10);
+    }
+    // everybody is done with tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        tc_fence_after();
+        tc_tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_encode() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+        return pb_fail("gemm_tc: the driver does not offer cuTensorMapEncodeTiled (%s)", cudaGetErrorString(e));
+    g_encode = (EncodeTiledFn)fn;
+    return 0;
+}
+
+// a [rows, K] bfloat16 matrix with row stride ld (elements), boxes of {64 k, box_rows}
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return pb_fail("gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d ld=%lld)", (int)r, rows, K, ld);
+    return 0;
+}
+
+static int g_tc_sms = 0;
+static int tc_sms() {
+    if (g_tc_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_tc_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_tc_sms <= 0) g_tc_sms = 148;
+    }
+    return g_tc_sms;
+}
+
+static int pick_bn(int rows_b) { return rows_b <= 16 ? 16 : rows_b <= 32 ? 32 : rows_b <= 64 ? 64 : rows_b <= 128 ? 128 : 256; }
+
+#define TC_MAX_TILES 65536    // arrival counters sit at the start of the scratch, partial tiles after them
+
+static void tc_plan(int rows_a, int rows_b, int K, int* bn, int* tiles_a, int* tiles_b, int* kblocks, int* ipb, int* blocks) {
+    *bn = pick_bn(rows_b);
+    *tiles_a = (rows_a + TC_BM - 1) / TC_BM;
+    *tiles_b = (rows_b + *bn - 1) / *bn;
+    *kblocks = (K + TC_BK - 1) / TC_BK;
+    const long long items = (long long)*tiles_a * *tiles_b * *kblocks;
+    long long b = tc_sms();
+    if (b > items) b = items;
+    *ipb = (int)((items + b - 1) / b);
+    *blocks = (int)((items + *ipb - 1) / *ipb);
+}
+
+// Whether the kernel takes the shape: 16-byte aligned rows (K and both row strides multiples of 8).
+PB_API int pb_gemm_tc_supported(int rows_a, int rows_b, int K, long long lda, long long ldb) {
+    if (rows_a < 1 || rows_b < 1 || K < 8 || K % 8 || lda % 8 || ldb % 8) return 0;
+    long long tiles = (long long)((rows_a + TC_BM - 1) / TC_BM) * ((rows_b + pick_bn(rows_b) - 1) / pick_bn(rows_b));
+    return tiles <= TC_MAX_TILES;
+}
+
+// Bytes of scratch a call needs: TC_MAX_TILES counters, then two partial tiles per block.
+PB_API long long pb_gemm_tc_scratch_bytes(int rows_a, int rows_b, int K) {
+    int bn, ta, tb, kb, ipb, blocks;
+    tc_plan(rows_a, rows_b, K, &bn, &ta, &tb, &kb, &ipb, &blocks);
+    return (long long)TC_MAX_TILES * 4 + (long long)blocks * 2 * TC_BM * bn * 4;
+}
+
+template <int BN>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int blocks, cudaStream_t stream) {
+    using S = TcShared<BN>;
+    static bool configured = false;
+    const size_t smem = (size_t)S::STAGES * S::STAGE_BYTES + 1024;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return pb_fail("gemm_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    pb_launch(gemm_tc_kernel<BN>, dim3(blocks), dim3(TC_THREADS), smem, stream, ma, mb, p);
+    return 0;
+}
+
+// C = A B^T.  transposed = 0: out[i * ldo + j] = C[i, j];  transposed = 1: out[j * ldo + i] = C[i, j].
+// bias: per feature (per column of out), float32 or null.  out_f32: 1 for float32 output, 0 for bfloat16.
+// scratch: pb_gemm_tc_scratch_bytes(...) bytes whose first 4 * TC_MAX_TILES bytes (the counters) are zero
+// before the first call; every call leaves them zero, so calls on one stream may share the buffer.
+PB_API int pb_gemm_tc_bf16(const void* A, const void* B, const float* bias, void* out, int rows_a, int rows_b, int K,
+                           long long lda, long long ldb, long long ldo, int transposed, int out_f32, void* scratch,
+                           int* status, cudaStream_t stream) {
+    PB_REQUIRE(pb_gemm_tc_supported(rows_a, rows_b, K, lda, ldb),
+               "gemm_tc: rows_a=%d rows_b=%d K=%d lda=%lld ldb=%lld not taken (rows must be 16-byte aligned)", rows_a, rows_b, K, lda, ldb);
+    PB_REQUIRE(A && B && out && scratch && pb_aligned(A, 16) && pb_aligned(B, 16), "gemm_tc: null or unaligned pointer");
+    if (int e = get_encode()) return e;
+    TcParams p{};
+    int bn, blocks;
+    tc_plan(rows_a, rows_b, K, &bn, &p.tiles_a, &p.tiles_b, &p.kblocks, &p.items_per_block, &blocks);
+    p.out = out; p.bias = bias; p.status = status; p.ldo = ldo; p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
+    p.transposed = transposed; p.out_f32 = out_f32;
+    p.counters = (int*)scratch;
+    p.scratch = (float*)((char*)scratch + (size_t)TC_MAX_TILES * 4);
+    CUtensorMap ma, mb;
+    if (int e = make_map(&ma, A, rows_a, K, lda, TC_BM)) return e;
+    if (int e = make_map(&mb, B, rows_b, K, ldb, bn)) return e;
+    int e = bn == 16 ? tc_launch<16>(ma, mb, p, blocks, stream)
+          : bn == 32 ? tc_launch<32>(ma, mb, p, blocks, stream)
+          : bn == 64 ? tc_launch<64>(ma, mb, p, blocks, stream)
+          : bn == 128 ? tc_launch<128>(ma, mb, p, blocks, stream) : tc_launch<256>(ma, mb, p, blocks, stream);
+    if (e) return e;
+    PB_CHECK_LAUNCH("gemm_tc");
+    return 0;
+}

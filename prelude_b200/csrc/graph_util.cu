@@ -11,6 +11,8 @@
 // dst[idx[i]] = val[i]; an index outside [0, dst_len) is skipped and raises *status.
 __global__ void scatter_i32_kernel(int32_t* __restrict__ dst, long long dst_len, const int32_t* __restrict__ idx,
                                    const int32_t* __restrict__ val, int n, int* __restrict__ status) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     long long at = idx[i];
@@ -26,7 +28,7 @@ PB_API int pb_scatter_i32(int32_t* dst, long long dst_len, const int32_t* idx, c
     PB_REQUIRE(n >= 0 && dst_len >= 0, "scatter_i32: bad sizes");
     if (n == 0) return 0;
     PB_REQUIRE(dst && idx && val, "scatter_i32: null pointer");
-    scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, dst_len, idx, val, n, status);
+    pb_launch(scatter_i32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, dst, dst_len, idx, val, n, status);
     PB_CHECK_LAUNCH("scatter_i32");
     return 0;
 }
@@ -37,6 +39,8 @@ PB_API int pb_scatter_i32(int32_t* dst, long long dst_len, const int32_t* idx, c
 __global__ void decode_advance_kernel(int32_t* __restrict__ tokens, int32_t* __restrict__ positions,
                                       long long* __restrict__ counters, const int32_t* __restrict__ sampled, int n,
                                       int max_positions) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     tokens[i] = sampled[i];
@@ -48,7 +52,7 @@ PB_API int pb_decode_advance(int32_t* tokens, int32_t* positions, long long* cou
                              int max_positions, cudaStream_t stream) {
     PB_REQUIRE(n >= 0 && tokens && positions && sampled, "decode_advance: bad arguments");
     if (n == 0) return 0;
-    decode_advance_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, positions, counters, sampled, n, max_positions);
+    pb_launch(decode_advance_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, positions, counters, sampled, n, max_positions);
     PB_CHECK_LAUNCH("decode_advance");
     return 0;
 }

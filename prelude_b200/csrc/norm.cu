@@ -28,6 +28,8 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 template <typename TX, typename TY>
 __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__ res, const float* __restrict__ w,
                                    TY* __restrict__ y, int width, float eps) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float red[32];
     size_t row = blockIdx.x;
     float* r = res + row * width;
@@ -56,6 +58,8 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
 template <typename TX, typename TY, int ITERS>
 __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, float* __restrict__ res, const float* __restrict__ w,
                                         TY* __restrict__ y, int width, float eps) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float red[32];
     size_t row = blockIdx.x;
     float4* r4 = reinterpret_cast<float4*>(res + row * width);
@@ -123,13 +127,13 @@ static int launch_add_rmsnorm(const void* x, float* res, const float* w, void* y
     if (vec) {
         int iters = (width / 4 + threads - 1) / threads;
         if (iters <= 2)
-            add_rmsnorm_vec4_kernel<TX, TY, 2><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 2>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
         else if (iters <= 4)
-            add_rmsnorm_vec4_kernel<TX, TY, 4><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 4>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
         else
-            add_rmsnorm_vec4_kernel<TX, TY, 8><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 8>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
     } else {
-        add_rmsnorm_kernel<TX, TY><<<rows, threads, 0, stream>>>((const TX*)x, res, w, (TY*)y, width, eps);
+        pb_launch(add_rmsnorm_kernel<TX, TY>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
     }
     return 0;
 }
@@ -155,6 +159,8 @@ template <typename TX, typename TY>
 __global__ void gather_add_rmsnorm_kernel(const TX* __restrict__ x, const float* __restrict__ res,
                                           const int32_t* __restrict__ rows, const float* __restrict__ w,
                                           TY* __restrict__ y, int width, int n_rows_total, float eps) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float red[32];
     const int src = rows[blockIdx.x];
     TY* out = y + (size_t)blockIdx.x * width;
@@ -183,7 +189,7 @@ PB_API int pb_gather_add_rmsnorm(const void* x, const float* res, const int32_t*
     PB_REQUIRE(res && rows && w && y, "gather_add_rmsnorm: null pointer");
     if (n_out == 0) return 0;
     PB_DISPATCH_DTYPE(dtype, T,
-        (gather_add_rmsnorm_kernel<T, T><<<n_out, norm_threads(width), 0, stream>>>(
+        (pb_launch(gather_add_rmsnorm_kernel<T, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream, 
             (const T*)x, res, rows, w, (T*)y, width, n_rows_total, eps)));
     PB_CHECK_LAUNCH("gather_add_rmsnorm");
     return 0;
@@ -194,6 +200,8 @@ PB_API int pb_gather_add_rmsnorm(const void* x, const float* res, const int32_t*
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y, int width,
                                float eps) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float red[32];
     size_t row = blockIdx.x;
     const T* xr = x + row * width;
@@ -213,7 +221,7 @@ PB_API int pb_rmsnorm(const void* x, const float* w, void* y, int dtype, int row
     PB_REQUIRE(x && w && y, "rmsnorm: null pointer");
     if (rows == 0) return 0;
     PB_DISPATCH_DTYPE(dtype, T,
-        (rmsnorm_kernel<T><<<rows, norm_threads(width), 0, stream>>>((const T*)x, w, (T*)y, width, eps)));
+        (pb_launch(rmsnorm_kernel<T>, dim3(rows), dim3(norm_threads(width)), 0, stream, (const T*)x, w, (T*)y, width, eps)));
     PB_CHECK_LAUNCH("rmsnorm");
     return 0;
 }

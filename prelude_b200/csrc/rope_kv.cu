@@ -28,6 +28,8 @@ __global__ void qknorm_rope_kvwrite_kernel(
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
     int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv, int* __restrict__ status) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     const int heads_per_token = n_heads + (write_kv ? 2 * n_kv_heads : 0);
     const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -114,7 +116,7 @@ PB_API int pb_qknorm_rope_kvwrite(
     long long blocks = (warps * 32 + threads - 1) / threads;
     PB_REQUIRE(blocks < (1ll << 31), "qknorm_rope_kvwrite: too many rows");
     PB_DISPATCH_DTYPE(dtype, T,
-        (qknorm_rope_kvwrite_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>(
+        (pb_launch(qknorm_rope_kvwrite_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream, 
             (const T*)q, (const T*)k, (const T*)v, token_stride, (T*)q_out, (T*)k_pages, (T*)v_pages, q_weight,
             k_weight, eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq, block_table,
             table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, write_kv, status)));

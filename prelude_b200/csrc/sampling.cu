@@ -78,6 +78,8 @@ PB_API long long pb_sample_scratch_floats(int rows, int vocab) { return (long lo
 __global__ void __launch_bounds__(PART_THREADS) sample_partial_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     float* __restrict__ part) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ ArgPair smem[32];
     __shared__ float red[32];
     const int nblk = gridDim.x, b = blockIdx.x, r = blockIdx.y;
@@ -131,6 +133,8 @@ __global__ void __launch_bounds__(PART_THREADS) sample_final_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ counters, const float* __restrict__ part,
     int nblk, int32_t* __restrict__ out) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ float sums[PART_THREADS];
     __shared__ float s_top, s_target;
     __shared__ int s_chunk, s_best, s_winner;
@@ -205,8 +209,8 @@ static int launch_two_pass(const float* logits, long long row_stride, int rows, 
                            const uint64_t* seeds, const uint64_t* counters, float* scratch, int32_t* out,
                            cudaStream_t stream) {
     const int nblk = part_blocks(vocab);
-    sample_partial_kernel<<<dim3(nblk, rows), PART_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, scratch);
-    sample_final_kernel<<<rows, PART_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, seeds, counters,
+    pb_launch(sample_partial_kernel, dim3(nblk, rows), dim3(PART_THREADS), 0, stream, logits, row_stride, vocab, temperature, scratch);
+    pb_launch(sample_final_kernel, dim3(rows), dim3(PART_THREADS), 0, stream, logits, row_stride, vocab, temperature, seeds, counters,
                                                            scratch, nblk, out);
     return 0;
 }
@@ -237,6 +241,8 @@ PB_API int pb_sample(const float* logits, long long row_stride, int rows, int vo
 __global__ void __launch_bounds__(SAMP_THREADS) softmax_temperature_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     float* __restrict__ probs) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
     __shared__ ArgPair smem[32];
     __shared__ float red[32];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
@@ -262,7 +268,7 @@ PB_API int pb_softmax_temperature(const float* logits, long long row_stride, int
                                   const float* temperature, float* probs, cudaStream_t stream) {
     PB_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "softmax_temperature: bad sizes");
     if (rows == 0) return 0;
-    softmax_temperature_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, probs);
+    pb_launch(softmax_temperature_kernel, dim3(rows), dim3(SAMP_THREADS), 0, stream, logits, row_stride, vocab, temperature, probs);
     PB_CHECK_LAUNCH("softmax_temperature");
     return 0;
 }

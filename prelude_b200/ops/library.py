@@ -46,6 +46,9 @@ _SIGNATURES = {
     "pb_gemm_skinny_scratch_bytes": ([I, I, I], L),
     "pb_gemm_skinny_supported": ([I, I, I, L, L], I),
     "pb_gemm_skinny_bf16": ([P, P, P, P, I, I, I, L, L, L, P, P], I),
+    "pb_gemm_tc_supported": ([I, I, I, L, L], I),
+    "pb_gemm_tc_scratch_bytes": ([I, I, I], L),
+    "pb_gemm_tc_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, P, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
     "pb_decode_advance": ([P, P, P, P, I, I, P], I),
 }
