@@ -236,8 +236,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a Rust workspace with git-only dependencies; no cargo/rustc and no network here, "
-                          "so it cannot be built or installed offline"}))
+                          "pip install of the reference fails (not installable: neither setup.py nor pyproject.toml; a Rust workspace with git-only "
+                          "dependencies, no cargo or rustc and no network here)"}))
         return 0
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus N with N > 1 is not supported")

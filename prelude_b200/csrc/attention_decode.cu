@@ -30,7 +30,6 @@
 //    zero for the next call.
 #include "attention_common.cuh"
 
-#define DEC_STAGES 3
 #define DEC_MAX_PAGES 512       // page ids of one block's share kept in shared memory (else read from the table)
 
 struct DecodeParams {
@@ -39,18 +38,20 @@ struct DecodeParams {
     int page_shift;             // log2(page_size) when it is a power of two, else -1
 };
 
-template <int DMAX>
+// BNW keys per warp tile, WST stages per warp
+template <int DMAX, int BNW, int WST>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams dp) {
     pb_grid_dep_launch();
     const AttnParams& p = dp.a;
     constexpr int STRIDE = DMAX + 8;
     constexpr int KSTEPS = DMAX / 16;
-    constexpr int STAGE_ELEMS = 2 * BN * STRIDE;            // K rows then V rows
+    constexpr int NT = BNW / 8;                              // 8-key score tiles per warp tile
+    constexpr int STAGE_ELEMS = 2 * BNW * STRIDE;            // K rows then V rows
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* sKV = sQ + 16 * STRIDE;
-    int32_t* s_pages = reinterpret_cast<int32_t*>(sKV + DEC_STAGES * STAGE_ELEMS);
-    __shared__ __align__(8) uint64_t bars[DEC_STAGES];
+    __nv_bfloat16* sKV = sQ + 16 * STRIDE;                   // [4 warps][WST stages][K, V][BNW rows]
+    int32_t* s_pages = reinterpret_cast<int32_t*>(sKV + 4 * WST * STAGE_ELEMS);
+    __shared__ __align__(8) uint64_t bars[4][WST];
     __shared__ int s_last;
 
     const int G = p.group, d = p.head_dim;
@@ -69,11 +70,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
     float o[DMAX / 8][4];
 #pragma unroll
     for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    bool healthy = true;
 
     if (kt0 <= kt1) {
         if (threadIdx.x == 0) {
 #pragma unroll
-            for (int s = 0; s < DEC_STAGES; ++s) mbar_init(&bars[s], 1);
+            for (int w = 0; w < 4; ++w)
+#pragma unroll
+                for (int s = 0; s < WST; ++s) mbar_init(&bars[w][s], 1);
             mbar_fence_init();
         }
         // page ids of keys [key_first, key_last] of this block
@@ -94,81 +98,102 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
             cp_async16(sQ + row * STRIDE + ch * 8, p.q + src, ok);
         }
         cp_async_commit();
-        __syncthreads();                                    // barriers and s_pages are ready
+        cp_async_wait<0>();
+        __syncthreads();                                    // barriers, s_pages and q are ready
 
-        // every thread brings one row of every tile: threads 0..63 a key row, 64..127 a value row
-        const int my_row = threadIdx.x & (BN - 1);
-        const bool my_is_v = threadIdx.x >= BN;
-        const __nv_bfloat16* my_src = (my_is_v ? p.v_pages : p.k_pages) + (size_t)kvh * d;
+        // From here on the four warps run on their own: warp w takes the BNW-key tiles w, w + 4, ...
+        // of the block's share, brings them in itself (lane i copies key row i and value row i of a
+        // tile with one bulk copy each) and waits on its own barriers.
+        const int first_wt = kt0 * (BN / BNW), last_wt = kt1 * (BN / BNW) + (BN / BNW) - 1;
         const size_t slot_elems = (size_t)p.n_kv_heads * d;
         const unsigned row_bytes = (unsigned)d * 2;
-        auto issue_tile = [&](int kt) {
-            const int stage = (kt - kt0) % DEC_STAGES;
-            uint64_t* bar = &bars[stage];
-            if (threadIdx.x == 0) {
-                const int n_valid = min(kv_end, kt * BN + BN) - max(lo, kt * BN);
-                mbar_arrive_expect_tx(bar, (unsigned)n_valid * row_bytes * 2);
-            }
-            __nv_bfloat16* dst = sKV + stage * STAGE_ELEMS + (my_is_v ? BN * STRIDE : 0) + my_row * STRIDE;
-            const int j = kt * BN + my_row;
-            if (j >= lo && j < kv_end) {
-                const int pi = dp.page_shift >= 0 ? (j >> dp.page_shift) : (j / ps);
-                int page = pages_in_smem ? s_pages[pi - page_first] : table[pi];
-                int slot = page * ps + (j - pi * ps);
-                if (page < 0 || page >= p.num_pages) {      // never read outside the pool; the step is reported as bad
-                    slot = 0;
-                    if (p.status) atomicExch(p.status, 6);
+        __nv_bfloat16* my_stages = sKV + warp * WST * STAGE_ELEMS;
+        auto issue_tile = [&](int wt, int use) {
+            const int stage = use % WST;
+            uint64_t* bar = &bars[warp][stage];
+            const int key0 = wt * BNW;
+            const int n_valid = max(0, min(kv_end, key0 + BNW) - max(lo, key0));
+            if (lane == 0) mbar_arrive_expect_tx(bar, (unsigned)n_valid * row_bytes * 2);
+            __nv_bfloat16* dk = my_stages + stage * STAGE_ELEMS + lane * STRIDE;
+            __nv_bfloat16* dv = dk + BNW * STRIDE;
+            const int j = key0 + lane;
+            if (lane < BNW) {
+                if (j >= lo && j < kv_end) {
+                    const int pi = dp.page_shift >= 0 ? (j >> dp.page_shift) : (j / ps);
+                    int page = pages_in_smem ? s_pages[pi - page_first] : table[pi];
+                    int slot = page * ps + (j - pi * ps);
+                    if (page < 0 || page >= p.num_pages) {  // never read outside the pool; the step is reported as bad
+                        slot = 0;
+                        if (p.status) atomicExch(p.status, 6);
+                    }
+                    const size_t off = (size_t)slot * slot_elems + (size_t)kvh * d;
+                    fence_proxy_async();
+                    bulk_copy_g2s(dk, p.k_pages + off, row_bytes, bar);
+                    bulk_copy_g2s(dv, p.v_pages + off, row_bytes, bar);
+                } else {
+                    // a value row that no key stands for: zeros, so that 0 * (whatever was there) cannot make a NaN
+                    for (int c = 0; c < chunks; ++c) *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
                 }
-                fence_proxy_async();
-                bulk_copy_g2s(dst, my_src + (size_t)slot * slot_elems, row_bytes, bar);
-            } else if (my_is_v) {
-                // a value row that no key stands for: zeros, so that 0 * (whatever was there) cannot make a NaN
-                for (int c = 0; c < chunks; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
             }
+            __syncwarp();
         };
-#pragma unroll
-        for (int i = 0; i < DEC_STAGES - 1; ++i)
-            if (kt0 + i <= kt1) issue_tile(kt0 + i);
-        cp_async_wait<0>();                                 // q
-        bool healthy = true;
-        int kt = kt0;
-        for (; kt <= kt1; ++kt) {
-            if (kt + DEC_STAGES - 1 <= kt1) issue_tile(kt + DEC_STAGES - 1);
-            const int use = kt - kt0;
-            const bool landed = mbar_wait_bounded(&bars[use % DEC_STAGES], (use / DEC_STAGES) & 1);
-            if (!__syncthreads_and(landed)) {               // gave up waiting: report, do not hang
+        // tiles that hold no visible key at all (before the window, after the last key) are skipped
+        int wt = first_wt + warp, use = 0, ahead_wt = wt, ahead_use = 0;
+        auto tile_has_keys = [&](int t) { return t * BNW + BNW > lo && t * BNW < kv_end; };
+        while (wt <= last_wt && !tile_has_keys(wt)) wt += 4;
+        ahead_wt = wt;
+#pragma unroll 1
+        for (int i = 0; i < WST - 1 && ahead_wt <= last_wt; ++i) {
+            issue_tile(ahead_wt, ahead_use++);
+            do { ahead_wt += 4; } while (ahead_wt <= last_wt && !tile_has_keys(ahead_wt));
+        }
+#pragma unroll 1
+        for (; wt <= last_wt; ++use) {
+            if (ahead_wt <= last_wt) {
+                issue_tile(ahead_wt, ahead_use++);
+                do { ahead_wt += 4; } while (ahead_wt <= last_wt && !tile_has_keys(ahead_wt));
+            }
+            const bool landed = mbar_wait_bounded(&bars[warp][use % WST], (use / WST) & 1);
+            if (!__all_sync(0xffffffffu, landed)) {         // gave up waiting: report, do not hang
                 healthy = false;
                 break;
             }
-            const __nv_bfloat16* sK = sKV + (use % DEC_STAGES) * STAGE_ELEMS;
-            const __nv_bfloat16* sV = sK + BN * STRIDE;
-            float s[2][4];
+            const __nv_bfloat16* sK = my_stages + (use % WST) * STAGE_ELEMS;
+            const __nv_bfloat16* sV = sK + BNW * STRIDE;
+            float s[NT][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; ++kk) {
                 if (kk * 16 < d) {
-                    unsigned a[4], b0, b1, b2, b3;
+                    unsigned a[4];
                     ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
-                    const int key = warp * 16 + (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
-                    ldmatrix_x4(b0, b1, b2, b3, sK + key * STRIDE + col);
-                    mma_bf16(s[0], a, b0, b1);
-                    mma_bf16(s[1], a, b2, b3);
+#pragma unroll
+                    for (int n2 = 0; n2 < NT / 2; ++n2) {
+                        unsigned b0, b1, b2, b3;
+                        const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
+                        ldmatrix_x4(b0, b1, b2, b3, sK + key * STRIDE + col);
+                        mma_bf16(s[2 * n2], a, b0, b1);
+                        mma_bf16(s[2 * n2 + 1], a, b2, b3);
+                    }
                 }
             }
-            const bool edge = kt * BN < lo || kt * BN + BN - 1 > pos;    // some key of the tile is not visible
+            const int key0 = wt * BNW;
+            const bool edge = key0 < lo || key0 + BNW - 1 > pos;           // some key of the tile is not visible
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int j = kt * BN + warp * 16 + nt * 8 + 2 * t4 + (e & 1);
+                    const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
                     s[nt][e] = (!edge || (j >= lo && j <= pos)) ? s[nt][e] * p.scale_log2 : -INFINITY;
                 }
             }
             float corr[2], mref[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                float rmax = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
+                float rmax = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) rmax = fmaxf(rmax, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
                 rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
                 rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
                 const float m_new = fmaxf(m[h], rmax);
@@ -178,7 +203,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
                 l[h] *= corr[h];
             }
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float pv = exp2f(s[nt][e] - mref[e >> 1]);
@@ -193,28 +218,31 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
                     o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
                 }
             }
-            unsigned a[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                             pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
 #pragma unroll
-            for (int d2 = 0; d2 < KSTEPS; ++d2) {
-                if (d2 * 16 < d) {
-                    unsigned b0, b1, b2, b3;
-                    const int key = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
-                    ldmatrix_x4_trans(b0, b1, b2, b3, sV + key * STRIDE + col);
-                    mma_bf16(o[2 * d2], a, b0, b1);
-                    mma_bf16(o[2 * d2 + 1], a, b2, b3);
+            for (int ks = 0; ks < BNW / 16; ++ks) {
+                unsigned a[4] = {pack_bf16(s[2 * ks][0], s[2 * ks][1]), pack_bf16(s[2 * ks][2], s[2 * ks][3]),
+                                 pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]), pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+#pragma unroll
+                for (int d2 = 0; d2 < KSTEPS; ++d2) {
+                    if (d2 * 16 < d) {
+                        unsigned b0, b1, b2, b3;
+                        const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
+                        ldmatrix_x4_trans(b0, b1, b2, b3, sV + key * STRIDE + col);
+                        mma_bf16(o[2 * d2], a, b0, b1);
+                        mma_bf16(o[2 * d2 + 1], a, b2, b3);
+                    }
                 }
             }
-            __syncthreads();                                // the stage may be refilled
+            __syncwarp();                                   // the stage may be refilled by this warp
+            do { wt += 4; } while (wt <= last_wt && !tile_has_keys(wt));
         }
         if (!healthy) {
-            if (threadIdx.x == 0 && p.status) atomicExch(p.status, 7);
+            if (lane == 0 && p.status) atomicExch(p.status, 7);
             // copies that were issued may still be in flight: give them a bounded time to land before
             // shared memory is used for something else
-            for (int t = kt; t <= min(kt1, kt + DEC_STAGES - 2); ++t)
-                mbar_wait_bounded(&bars[(t - kt0) % DEC_STAGES], ((t - kt0) / DEC_STAGES) & 1);
-            __syncthreads();
+            for (int u = use; u < ahead_use; ++u) mbar_wait_bounded(&bars[warp][u % WST], (u / WST) & 1);
         }
+        __syncthreads();                                    // all warps are done with the tile buffers
     }
     pb_grid_dep_wait();                                     // blocks without keys come here directly
     // merge the four warps through shared memory (the tile buffers are free now)
@@ -289,8 +317,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
     }
 }
 
+// keys per warp tile and stages per warp, by head size: as much in flight as shared memory holds
+template <int DMAX> struct DecodeTiling { static constexpr int BNW = 32, WST = 3; };
+template <> struct DecodeTiling<256> { static constexpr int BNW = 16, WST = 3; };
+
 template <int DMAX> static size_t decode_smem() {
-    size_t tiles = (size_t)(16 + DEC_STAGES * 2 * BN) * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
+    using T = DecodeTiling<DMAX>;
+    size_t tiles = (size_t)(16 + 4 * T::WST * 2 * T::BNW) * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
     size_t merge = (size_t)16 * (DMAX + 8) * 2 + (size_t)(4 * 16 * DMAX + 128) * 4;
     return tiles > merge ? tiles : merge;
 }
@@ -300,11 +333,12 @@ static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
     static bool configured = false;
     size_t smem = decode_smem<DMAX>();
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DMAX, DecodeTiling<DMAX>::BNW, DecodeTiling<DMAX>::WST>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return pb_fail("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    pb_launch(attn_decode_kernel<DMAX>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(ATT_THREADS), smem, stream, dp);
+    pb_launch(attn_decode_kernel<DMAX, DecodeTiling<DMAX>::BNW, DecodeTiling<DMAX>::WST>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(ATT_THREADS), smem, stream, dp);
     return 0;
 }
 

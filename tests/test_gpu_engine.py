@@ -99,3 +99,20 @@ def test_f32_cuts_agree_bitwise(folders, which):
     for other in results[1:]:
         for key, row in results[0].items():
             assert torch.equal(row, other[key]), f"{key}: cuts disagree by {(row - other[key]).abs().max():.3e}"
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "mixed"])
+def test_bf16_with_every_product_on_the_tcgen05_kernel(folders, monkeypatch, which, cut):
+    """The same comparison with all linear layers (prompt portions and decode steps) on the
+    library's own tensor-core product instead of cuBLAS."""
+    from prelude_b200.ops import linear
+    monkeypatch.setattr(linear, "TC_POLICY", "all")
+    folder = folders[(which, torch.bfloat16)]
+    reqs = _requests(which)
+    ref = _reference(which, folder, reqs)
+    page = tiny.PARAMS[which][2]
+    schedule = {"whole": harness.whole, "tail_decode": harness.tail_decode, "mixed": harness.mixed}[cut](reqs)
+    runner = _runner(folder, torch.bfloat16, page, harness.peak_tokens(schedule, page) // page)
+    _compare(harness.run_schedule(runner, schedule), ref, torch.bfloat16)
+    assert int(linear.tc_status(torch.device("cuda:0")).item()) == 0

@@ -450,3 +450,35 @@ def test_gemm_skinny_refuses_other_shapes_and_linear_falls_back():
     assert (linear(x, w).double() - want).abs().max() <= tol(torch.bfloat16, float(want.abs().max()))
     assert not skinny_takes(rnd(100, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
     assert skinny_takes(rnd(8, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
+
+
+# ---------------------------------------------------------------------------------------
+# the tcgen05 product (TMA, tensor memory), in both orientations
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K_", [(8, 128, 64), (1, 2560, 4096), (8, 6144, 2560), (5, 200, 72), (33, 2560, 9728),
+                                    (64, 1000, 1024), (16, 331, 200), (65, 256, 64), (128, 256, 256), (300, 2560, 4096),
+                                    (2048, 6144, 2560), (130, 331, 200), (1000, 19456, 2560)])
+def test_gemm_tc_against_float32(M, N, K_):
+    from prelude_b200.ops.linear import gemm_tc, tc_status
+    x, w, b = rnd(M, K_, dtype=torch.bfloat16, seed=31), rnd(N, K_, dtype=torch.bfloat16, seed=32, scale=0.05), rnd(N, seed=33)
+    want = x.float() @ w.float().T
+    scale = float(want.abs().max())
+    got = gemm_tc(x, w)
+    assert got.dtype == torch.bfloat16 and (got.float() - want).abs().max() <= tol(torch.bfloat16, scale)
+    got32 = gemm_tc(x, w, b, torch.float32)
+    assert got32.dtype == torch.float32 and (got32 - (want + b)).abs().max() <= 2e-5 * scale * 4
+    assert torch.equal(gemm_tc(x, w), got)                           # counters back at zero, the same sums again
+    wide = rnd(M, K_ + 64, dtype=torch.bfloat16, seed=34)            # x as a view into a wider tensor
+    assert torch.equal(gemm_tc(wide[:, 32:32 + K_], w), gemm_tc(wide[:, 32:32 + K_].contiguous(), w))
+    assert int(tc_status(x.device).item()) == 0
+
+
+def test_gemm_tc_refuses_unaligned_rows():
+    from prelude_b200.ops.library import KernelLibraryError
+    from prelude_b200.ops.linear import gemm_tc, linear, tc_takes
+    x, w = rnd(4, 68, dtype=torch.bfloat16), rnd(40, 68, dtype=torch.bfloat16)      # rows of 136 bytes
+    assert not tc_takes(x, w)
+    with pytest.raises(KernelLibraryError, match="not taken"):
+        gemm_tc(x, w)
+    want = x.double() @ w.double().T
+    assert (linear(x, w, None, torch.float32).double() - want).abs().max() <= 1e-3 * float(want.abs().max())
