@@ -11,7 +11,9 @@ holds one slot for its whole life, whether or not any layer uses it.
 Pages are taken when a request's token count grows (``grow``), given back when
 a window has passed them (``trim``) and when the request ends (``release``),
 and are then used again by whoever asks next.  The reference keeps one pool
-with per-layer tensors [pages, page_size, heads, head_dim]
+with per-layer tensors [pages, page_size, heads, head_dim]; here a page is laid out
+head by head, [pages, heads, page_size, head_dim], so that the keys (or values) of one head in one page
+are one contiguous run of memory, which is what the attention kernels fetch at a time
 (crates/prelude-core/src/scheduler/components/cache/manager.rs:286-329) and
 declares the per-layer needs that grouping rests on
 (crates/prelude-core/src/scheduler/components/cache/mod.rs:13-30).
@@ -104,7 +106,7 @@ class CacheManager:
     # -- device memory ----------------------------------------------------------------
     def _allocate_tensors(self) -> None:
         for g in self.groups:
-            shape = (self.num_pages, self.page_size, g.need.n_kv_heads, g.need.head_dim)
+            shape = (self.num_pages, g.need.n_kv_heads, self.page_size, g.need.head_dim)
             for n in g.members:
                 g.k_pages[n] = torch.zeros(shape, dtype=self.dtype, device=self.device)
                 g.v_pages[n] = torch.zeros(shape, dtype=self.dtype, device=self.device)

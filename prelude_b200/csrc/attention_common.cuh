@@ -73,7 +73,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 struct AttnParams {
     const __nv_bfloat16* q;        // [T, nH, D]
-    const __nv_bfloat16* k_pages;  // [pages, page_size, nKV, D]
+    const __nv_bfloat16* k_pages;  // [pages, nKV, page_size, D]
     const __nv_bfloat16* v_pages;
     __nv_bfloat16* out;            // [T, nH, D]
     const int32_t* block_table;    // [rows, table_stride]
@@ -90,6 +90,7 @@ struct AttnParams {
     int n_splits;
     int table_stride, page_size, num_pages;
     int n_tokens, n_heads, n_kv_heads, head_dim, group, window;
+    int swizzle;                   // pages store the 16-byte chunks of a token row permuted (see pb_kv_elem_offset)
     float scale_log2;              // scale * log2(e)
     int* status;
 };
@@ -114,7 +115,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* s
                 ok = false;
                 if (p.status) atomicExch(p.status, 6);
             } else {
-                src = (((size_t)page * p.page_size + j % p.page_size) * p.n_kv_heads + kvh) * p.head_dim + ch * 8;
+                const int in_page = j % p.page_size;
+                src = (((size_t)page * p.n_kv_heads + kvh) * p.page_size + in_page) * p.head_dim + (p.swizzle ? ((ch ^ (in_page & 7)) * 8) : ch * 8);
             }
         }
         cp_async16(sK + row * STRIDE + ch * 8, p.k_pages + src, ok);

@@ -9,27 +9,42 @@
 // crates/prelude-cuda/src/attn/flash_v4.rs:125-278, flashinfer.rs:766-793).
 //
 // A decode step is a stream over the cache: every key and value of every live
-// request is read once, so the kernel is arranged to keep many bytes in flight.
+// request is read once, so the kernel is arranged to keep many bytes in flight
+// and to keep the arithmetic out of the way of the loads.
 //  * A block owns one (token, key/value head) and a contiguous share of that
 //    request's 64-key tiles.  The G query heads of the group are the rows of the
 //    tensor-core tile, so the group's keys and values are read once.
-//  * Tiles come through a ring of three shared-memory stages, two tiles ahead of
-//    the one being used.  Every thread brings one row (one token's key or value
-//    of this head, head_dim * 2 bytes) per tile with one bulk asynchronous copy
-//    that completes on the stage's shared-memory barrier; the page ids of the
-//    block's whole share are fetched into shared memory first, so the copies do
-//    not wait on the block table.  Waits on a barrier are bounded: a block that
-//    gives up raises the step's status word and returns.
-//  * Each of the 4 warps takes 16 keys of every tile (scores, running maximum
-//    and sum in float32, probabilities rounded to bfloat16 for the second
-//    product); the warps are merged through shared memory at the end.
+//  * Tiles go into a ring of shared-memory stages with a full and an empty
+//    barrier each; as many tiles are in flight as shared memory holds.  The page
+//    ids of the block's whole share are fetched into shared memory first.
+//    Two ways of bringing a tile in:
+//      bulk - one head's tokens of one page are one contiguous run of memory
+//             (a few KB), stored with permuted 16-byte chunks (pb_kv_elem_offset);
+//             one lane fetches each run with a single bulk copy
+//             (cp.async.bulk) that completes on the stage's barrier, and the run
+//             lands in shared memory ready for conflict-free ldmatrix.  Measured
+//             on B200: 4 KB bulk copies reach the full memory bandwidth (42 GB/s
+//             per multiprocessor), 256-byte ones 9 GB/s, tensor-map boxes of 16
+//             rows x 128 bytes 22 GB/s, 16-byte copies through the load/store path
+//             about 25 GB/s.  Used when pages are permuted and page_size % 8 == 0.
+//      lsu  - four loader warps copy 16 bytes per lane (cp.async) into padded
+//             rows; any head size and page size.
+//  * Consumer warps (four; as many as there are stages when fewer fit) take whole
+//    64-key tiles in turn (tile i goes to warp i mod 4):
+//    scores, running maximum and sum in float32, probabilities rounded to
+//    bfloat16 for the second product.  No block-wide barrier in the loop.  The
+//    warps are merged through shared memory at the end.
 //  * With more than one split, every block writes its unnormalised partial
 //    result with its maximum and sum to scratch memory and counts itself in;
 //    the block that arrives last for a (token, key/value head) adds the splits
 //    up in ascending order and writes the output.  The counters are left at
 //    zero for the next call.
+//  * Waits on barriers are bounded in time: a warp that gives up raises the
+//    step's status word and goes on to the end.
 #include "attention_common.cuh"
 
+#define DEC_THREADS 256
+#define DEC_LOADERS 128
 #define DEC_MAX_PAGES 512       // page ids of one block's share kept in shared memory (else read from the table)
 
 struct DecodeParams {
@@ -38,21 +53,43 @@ struct DecodeParams {
     int page_shift;             // log2(page_size) when it is a power of two, else -1
 };
 
-// BNW keys per warp tile, WST stages per warp
-template <int DMAX, int BNW, int WST>
-__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams dp) {
+#define BNW 64                  // keys per consumer tile
+
+// One ring of stages shared by all warps; tile i lives in stage i % STAGES and is consumed by warp i % NC.
+// A barrier wait can tell only the current phase from the one before it, so a consumer must not start
+// to wait for tile i before tile i - STAGES (the stage's previous tenant) has been consumed: it first
+// waits until the loaders have announced tile i (s_issued), which they do only after that.
+template <int DMAX, bool BULK> struct DecodeTiling {
+    static constexpr int STRIDE = BULK ? DMAX : DMAX + 8;    // lsu: padded rows; bulk: dense rows with permuted chunks
+    static constexpr int STAGE_ELEMS = 2 * BNW * STRIDE;     // K rows then V rows
+    static constexpr int FIT = (200 * 1024) / (STAGE_ELEMS * 2);
+    static constexpr int STAGES = FIT > 8 ? 8 : FIT;
+    static constexpr int NC = STAGES < 4 ? STAGES : 4;       // consumer warps
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// the barrier gets this thread's arrival when all its earlier asynchronous copies have landed
+__device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int DMAX, bool BULK>
+__global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParams dp) {
     pb_grid_dep_launch();
+    using T = DecodeTiling<DMAX, BULK>;
     const AttnParams& p = dp.a;
-    constexpr int STRIDE = DMAX + 8;
+    constexpr int STRIDE = T::STRIDE;
     constexpr int KSTEPS = DMAX / 16;
-    constexpr int NT = BNW / 8;                              // 8-key score tiles per warp tile
-    constexpr int STAGE_ELEMS = 2 * BNW * STRIDE;            // K rows then V rows
+    constexpr int S = T::STAGES, NC = T::NC;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* sKV = sQ + 16 * STRIDE;                   // [4 warps][WST stages][K, V][BNW rows]
-    int32_t* s_pages = reinterpret_cast<int32_t*>(sKV + 4 * WST * STAGE_ELEMS);
-    __shared__ __align__(8) uint64_t bars[4][WST];
-    __shared__ int s_last;
+    __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    constexpr int QSTRIDE = DMAX + 8;
+    __nv_bfloat16* sQ = stages + S * T::STAGE_ELEMS;
+    int32_t* s_pages = reinterpret_cast<int32_t*>(sQ + 16 * QSTRIDE);
+    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S];
+    __shared__ int s_last, s_issued;
 
     const int G = p.group, d = p.head_dim;
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
@@ -70,14 +107,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
     float o[DMAX / 8][4];
 #pragma unroll
     for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    bool healthy = true;
 
     if (kt0 <= kt1) {
         if (threadIdx.x == 0) {
+            s_issued = 0;
 #pragma unroll
-            for (int w = 0; w < 4; ++w)
-#pragma unroll
-                for (int s = 0; s < WST; ++s) mbar_init(&bars[w][s], 1);
+            for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], BULK ? 1 : DEC_LOADERS); mbar_init(&empty_bar[s], 1); }
             mbar_fence_init();
         }
         // page ids of keys [key_first, key_last] of this block
@@ -85,174 +120,228 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
         const int page_first = key_first / ps, n_pages = key_last / ps - page_first + 1;
         const bool pages_in_smem = n_pages <= DEC_MAX_PAGES;
         if (pages_in_smem)
-            for (int i = threadIdx.x; i < n_pages; i += ATT_THREADS) s_pages[i] = table[page_first + i];
+            for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) s_pages[i] = table[page_first + i];
         // positions and block tables were written before the previous kernel started; q and the
         // newest keys and values are that kernel's output
         pb_grid_dep_wait();
         // q rows of the group (rows from G on are zero)
         const int chunks = d >> 3;
-        for (int c = threadIdx.x; c < 16 * chunks; c += ATT_THREADS) {
+        for (int c = threadIdx.x; c < 16 * chunks; c += DEC_THREADS) {
             const int row = c / chunks, ch = c - row * chunks;
             const bool ok = row < G;
             const size_t src = ok ? (((size_t)tok * p.n_heads + kvh * G + row) * d + ch * 8) : 0;
-            cp_async16(sQ + row * STRIDE + ch * 8, p.q + src, ok);
+            cp_async16(sQ + row * QSTRIDE + ch * 8, p.q + src, ok);
         }
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();                                    // barriers, s_pages and q are ready
 
-        // From here on the four warps run on their own: warp w takes the BNW-key tiles w, w + 4, ...
-        // of the block's share, brings them in itself (lane i copies key row i and value row i of a
-        // tile with one bulk copy each) and waits on its own barriers.
-        const int first_wt = kt0 * (BN / BNW), last_wt = kt1 * (BN / BNW) + (BN / BNW) - 1;
-        const size_t slot_elems = (size_t)p.n_kv_heads * d;
-        const unsigned row_bytes = (unsigned)d * 2;
-        __nv_bfloat16* my_stages = sKV + warp * WST * STAGE_ELEMS;
-        auto issue_tile = [&](int wt, int use) {
-            const int stage = use % WST;
-            uint64_t* bar = &bars[warp][stage];
-            const int key0 = wt * BNW;
-            const int n_valid = max(0, min(kv_end, key0 + BNW) - max(lo, key0));
-            if (lane == 0) mbar_arrive_expect_tx(bar, (unsigned)n_valid * row_bytes * 2);
-            __nv_bfloat16* dk = my_stages + stage * STAGE_ELEMS + lane * STRIDE;
-            __nv_bfloat16* dv = dk + BNW * STRIDE;
-            const int j = key0 + lane;
-            if (lane < BNW) {
-                if (j >= lo && j < kv_end) {
-                    const int pi = dp.page_shift >= 0 ? (j >> dp.page_shift) : (j / ps);
-                    int page = pages_in_smem ? s_pages[pi - page_first] : table[pi];
-                    int slot = page * ps + (j - pi * ps);
-                    if (page < 0 || page >= p.num_pages) {  // never read outside the pool; the step is reported as bad
-                        slot = 0;
-                        if (p.status) atomicExch(p.status, 6);
-                    }
-                    const size_t off = (size_t)slot * slot_elems + (size_t)kvh * d;
-                    fence_proxy_async();
-                    bulk_copy_g2s(dk, p.k_pages + off, row_bytes, bar);
-                    bulk_copy_g2s(dv, p.v_pages + off, row_bytes, bar);
-                } else {
-                    // a value row that no key stands for: zeros, so that 0 * (whatever was there) cannot make a NaN
-                    for (int c = 0; c < chunks; ++c) *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
-                }
-            }
-            __syncwarp();
+        const int n_tiles = (kt1 - kt0 + 1) * (BN / BNW);   // consumer tiles of BNW keys; tile i belongs to warp i % NC
+        const int key_base = kt0 * BN;
+        // row r, 16-byte chunk c of a key or value tile (dense permuted rows, or padded rows)
+        const int row_elems = BULK ? d : STRIDE;
+        auto tile_at = [&](const __nv_bfloat16* base, int r, int c) {
+            return base + r * row_elems + ((BULK ? (c ^ (r & 7)) : c) << 3);
         };
-        // tiles that hold no visible key at all (before the window, after the last key) are skipped
-        int wt = first_wt + warp, use = 0, ahead_wt = wt, ahead_use = 0;
-        auto tile_has_keys = [&](int t) { return t * BNW + BNW > lo && t * BNW < kv_end; };
-        while (wt <= last_wt && !tile_has_keys(wt)) wt += 4;
-        ahead_wt = wt;
+        if (BULK && warp >= 4) {
+            // ---------------- bulk loader: lane u of warp 4 fetches the u-th run of keys and of values ----------------
+            if (warp == 4) {
+                const int run_rows = min(ps, BNW);          // tokens one copy brings: a page's run, or BNW of it
+                const int runs = BNW / run_rows;
+                const unsigned run_bytes = (unsigned)run_rows * d * 2;
+                bool ok = true;
 #pragma unroll 1
-        for (int i = 0; i < WST - 1 && ahead_wt <= last_wt; ++i) {
-            issue_tile(ahead_wt, ahead_use++);
-            do { ahead_wt += 4; } while (ahead_wt <= last_wt && !tile_has_keys(ahead_wt));
-        }
-#pragma unroll 1
-        for (; wt <= last_wt; ++use) {
-            if (ahead_wt <= last_wt) {
-                issue_tile(ahead_wt, ahead_use++);
-                do { ahead_wt += 4; } while (ahead_wt <= last_wt && !tile_has_keys(ahead_wt));
-            }
-            const bool landed = mbar_wait_bounded(&bars[warp][use % WST], (use / WST) & 1);
-            if (!__all_sync(0xffffffffu, landed)) {         // gave up waiting: report, do not hang
-                healthy = false;
-                break;
-            }
-            const __nv_bfloat16* sK = my_stages + (use % WST) * STAGE_ELEMS;
-            const __nv_bfloat16* sV = sK + BNW * STRIDE;
-            float s[NT][4];
-#pragma unroll
-            for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-            for (int kk = 0; kk < KSTEPS; ++kk) {
-                if (kk * 16 < d) {
-                    unsigned a[4];
-                    ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
-#pragma unroll
-                    for (int n2 = 0; n2 < NT / 2; ++n2) {
-                        unsigned b0, b1, b2, b3;
-                        const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
-                        ldmatrix_x4(b0, b1, b2, b3, sK + key * STRIDE + col);
-                        mma_bf16(s[2 * n2], a, b0, b1);
-                        mma_bf16(s[2 * n2 + 1], a, b2, b3);
+                for (int i = 0; i < n_tiles; ++i) {
+                    const int stage = i % S;
+                    ok = mbar_wait_bounded(&empty_bar[stage], ((i / S) & 1) ^ 1);
+                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    if (lane == 0) *(volatile int*)&s_issued = i + 1;       // the stage's previous tenant has been consumed
+                    __nv_bfloat16* sK = stages + stage * T::STAGE_ELEMS;
+                    __nv_bfloat16* sV = sK + BNW * STRIDE;
+                    const int j0 = key_base + i * BNW + lane * run_rows;
+                    size_t src = 0;
+                    bool want = lane < runs && j0 <= pos && j0 + run_rows > lo;   // the run holds a visible key
+                    if (want) {
+                        const int pi = dp.page_shift >= 0 ? (j0 >> dp.page_shift) : (j0 / ps);
+                        const int page = pages_in_smem ? s_pages[pi - page_first] : table[pi];
+                        if (page < 0 || page >= p.num_pages) {
+                            want = false;                   // never read outside the pool; the step is reported as bad
+                            if (p.status) atomicExch(p.status, 6);
+                        } else {
+                            src = (((size_t)page * p.n_kv_heads + kvh) * ps + (j0 - pi * ps)) * d;
+                        }
+                    }
+                    const unsigned n_want = __popc(__ballot_sync(0xffffffffu, want));
+                    if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], n_want * run_bytes * 2);
+                    __syncwarp();
+                    if (want) {
+                        bulk_copy_g2s(sK + lane * run_rows * d, p.k_pages + src, run_bytes, &full_bar[stage]);
+                        bulk_copy_g2s(sV + lane * run_rows * d, p.v_pages + src, run_bytes, &full_bar[stage]);
                     }
                 }
+                if (!ok && lane == 0 && p.status) atomicExch(p.status, 7);
             }
-            const int key0 = wt * BNW;
-            const bool edge = key0 < lo || key0 + BNW - 1 > pos;           // some key of the tile is not visible
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
-                    s[nt][e] = (!edge || (j >= lo && j <= pos)) ? s[nt][e] * p.scale_log2 : -INFINITY;
-                }
-            }
-            float corr[2], mref[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float rmax = -INFINITY;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) rmax = fmaxf(rmax, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
-                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
-                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
-                const float m_new = fmaxf(m[h], rmax);
-                corr[h] = (m[h] == m_new) ? 1.f : ((m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new));
-                mref[h] = (m_new == -INFINITY) ? 0.f : m_new;
-                m[h] = m_new;
-                l[h] *= corr[h];
-            }
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float pv = exp2f(s[nt][e] - mref[e >> 1]);
-                    s[nt][e] = pv;
-                    l[e >> 1] += pv;
-                }
-            }
-            // the accumulator is rescaled only when some row's maximum moved
-            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
-#pragma unroll
-                for (int i = 0; i < DMAX / 8; ++i) {
-                    o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
-                }
-            }
-#pragma unroll
-            for (int ks = 0; ks < BNW / 16; ++ks) {
-                unsigned a[4] = {pack_bf16(s[2 * ks][0], s[2 * ks][1]), pack_bf16(s[2 * ks][2], s[2 * ks][3]),
-                                 pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]), pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3])};
-#pragma unroll
-                for (int d2 = 0; d2 < KSTEPS; ++d2) {
-                    if (d2 * 16 < d) {
-                        unsigned b0, b1, b2, b3;
-                        const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
-                        ldmatrix_x4_trans(b0, b1, b2, b3, sV + key * STRIDE + col);
-                        mma_bf16(o[2 * d2], a, b0, b1);
-                        mma_bf16(o[2 * d2 + 1], a, b2, b3);
+        } else if (warp >= 4) {
+            // ---------------- loaders: thread lt copies 16-byte chunk `ch` of rows row0, row0 + rows_per_pass, ... ----------------
+            const int lt = threadIdx.x - DEC_LOADERS;
+            const int rows_per_pass = DEC_LOADERS / chunks;
+            const int row0 = lt / chunks, ch = lt - row0 * chunks;
+            const bool copier = row0 < rows_per_pass;
+            const size_t head_elems = (size_t)ps * d;        // one head's run of a page
+            bool ok = true;
+#pragma unroll 1
+            for (int i = 0; i < n_tiles; ++i) {
+                const int stage = i % S;
+                ok = mbar_wait_bounded(&empty_bar[stage], ((i / S) & 1) ^ 1);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                if (lt == 0) *(volatile int*)&s_issued = i + 1;             // the stage's previous tenant has been consumed
+                __nv_bfloat16* sK = stages + stage * T::STAGE_ELEMS;
+                __nv_bfloat16* sV = sK + BNW * STRIDE;
+                if (copier) {
+                    for (int row = row0; row < BNW; row += rows_per_pass) {
+                        const int j = key_base + i * BNW + row;
+                        bool valid = j >= lo && j < kv_end;
+                        size_t src = 0;
+                        if (valid) {
+                            const int pi = dp.page_shift >= 0 ? (j >> dp.page_shift) : (j / ps);
+                            const int page = pages_in_smem ? s_pages[pi - page_first] : table[pi];
+                            if (page < 0 || page >= p.num_pages) {
+                                valid = false;              // never read outside the pool; the step is reported as bad
+                                if (p.status) atomicExch(p.status, 6);
+                            } else {
+                                const int in_page = j - pi * ps;
+                                src = ((size_t)page * p.n_kv_heads + kvh) * head_elems + (size_t)in_page * d +
+                                      ((p.swizzle ? (ch ^ (in_page & 7)) : ch) << 3);
+                            }
+                        }
+                        cp_async16(sK + row * STRIDE + ch * 8, p.k_pages + src, valid);   // rows without a key are zero-filled
+                        cp_async16(sV + row * STRIDE + ch * 8, p.v_pages + src, valid);
                     }
                 }
+                cp_async_arrive_on(&full_bar[stage]);
             }
-            __syncwarp();                                   // the stage may be refilled by this warp
-            do { wt += 4; } while (wt <= last_wt && !tile_has_keys(wt));
-        }
-        if (!healthy) {
-            if (lane == 0 && p.status) atomicExch(p.status, 7);
-            // copies that were issued may still be in flight: give them a bounded time to land before
-            // shared memory is used for something else
-            for (int u = use; u < ahead_use; ++u) mbar_wait_bounded(&bars[warp][u % WST], (u / WST) & 1);
+            if (!ok && lane == 0 && p.status) atomicExch(p.status, 7);
+            cp_async_wait<0>();                             // nothing of this thread is in flight when shared memory changes its use
+        } else {
+            // ---------------- consumers: warp w takes tiles w, w + NC, ... ----------------
+#pragma unroll 1
+            for (int i = warp; warp < NC && i < n_tiles; i += NC) {
+                const int stage = i % S;
+                bool landed = true;
+                if (*(volatile int*)&s_issued <= i) {       // not announced yet: the barrier may still be in an older phase
+                    const long long t0 = clock64();
+                    while (*(volatile int*)&s_issued <= i)
+                        if (clock64() - t0 > (1ll << 31)) { landed = false; break; }
+                }
+                landed = landed && mbar_wait_bounded(&full_bar[stage], (i / S) & 1);
+                if (!__all_sync(0xffffffffu, landed)) {     // gave up waiting: report, do not hang
+                    if (lane == 0 && p.status) atomicExch(p.status, 7);
+                    break;
+                }
+                const __nv_bfloat16* sK = stages + stage * T::STAGE_ELEMS;
+                const __nv_bfloat16* sV = sK + BNW * STRIDE;
+                const int key0 = key_base + i * BNW;
+                constexpr int NT = BNW / 8;
+                float s[NT][4];
+#pragma unroll
+                for (int q = 0; q < NT; ++q) s[q][0] = s[q][1] = s[q][2] = s[q][3] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    if (kk * 16 < d) {
+                        unsigned a[4];
+                        ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (lane & 15) * QSTRIDE + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                        for (int n2 = 0; n2 < NT / 2; ++n2) {
+                            unsigned b0, b1, b2, b3;
+                            const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7);
+                            ldmatrix_x4(b0, b1, b2, b3, tile_at(sK, key, kk * 2 + ((lane >> 3) & 1)));
+                            mma_bf16(s[2 * n2], a, b0, b1);
+                            mma_bf16(s[2 * n2 + 1], a, b2, b3);
+                        }
+                    }
+                }
+                const bool edge = key0 < lo || key0 + BNW - 1 > pos;         // some key of the tile is not visible
+                if (BULK && edge) {
+                    // value rows that no visible key stands for hold whatever the page (or the stage) held:
+                    // zeros instead, so that 0 * (whatever is there) cannot make a NaN
+                    for (int r = lane; r < BNW; r += 32) {
+                        const int j = key0 + r;
+                        if (j < lo || j > pos)
+                            for (int c = 0; c < (d >> 3); ++c)
+                                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(sV) + r * row_elems + c * 8) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async();                    // these ordinary stores come before the bulk copy that refills the stage
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
+                        s[nt][e] = (!edge || (j >= lo && j <= pos)) ? s[nt][e] * p.scale_log2 : -INFINITY;
+                    }
+                }
+                float corr[2], mref[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float rmax = -INFINITY;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) rmax = fmaxf(rmax, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
+                    rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+                    rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+                    const float m_new = fmaxf(m[h], rmax);
+                    corr[h] = (m[h] == m_new) ? 1.f : ((m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new));
+                    mref[h] = (m_new == -INFINITY) ? 0.f : m_new;
+                    m[h] = m_new;
+                    l[h] *= corr[h];
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pv = exp2f(s[nt][e] - mref[e >> 1]);
+                        s[nt][e] = pv;
+                        l[e >> 1] += pv;
+                    }
+                }
+                // the accumulator is rescaled only when some row's maximum moved
+                if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+                    for (int q = 0; q < DMAX / 8; ++q) {
+                        o[q][0] *= corr[0]; o[q][1] *= corr[0]; o[q][2] *= corr[1]; o[q][3] *= corr[1];
+                    }
+                }
+#pragma unroll
+                for (int ks = 0; ks < BNW / 16; ++ks) {
+                    unsigned a[4] = {pack_bf16(s[2 * ks][0], s[2 * ks][1]), pack_bf16(s[2 * ks][2], s[2 * ks][3]),
+                                     pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]), pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+#pragma unroll
+                    for (int d2 = 0; d2 < KSTEPS; ++d2) {
+                        if (d2 * 16 < d) {
+                            unsigned b0, b1, b2, b3;
+                            const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                            ldmatrix_x4_trans(b0, b1, b2, b3, tile_at(sV, key, d2 * 2 + (lane >> 4)));
+                            mma_bf16(o[2 * d2], a, b0, b1);
+                            mma_bf16(o[2 * d2 + 1], a, b2, b3);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[stage]);               // the stage may be refilled
+            }
         }
         __syncthreads();                                    // all warps are done with the tile buffers
     }
     pb_grid_dep_wait();                                     // blocks without keys come here directly
     // merge the four warps through shared memory (the tile buffers are free now)
-    float* sO = reinterpret_cast<float*>(sKV);              // [4][16][DMAX]
+    float* sO = reinterpret_cast<float*>(stages);           // [4][16][DMAX]
     float* sM = sO + 4 * 16 * DMAX;                         // [4][16]
     float* sL = sM + 64;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        if (warp >= 4) continue;                            // the loader warps hold no partial result
         const int row = g + 8 * h;
         if (t4 == 0) { sM[warp * 16 + row] = m[h]; sL[warp * 16 + row] = l[h]; }
 #pragma unroll
@@ -263,7 +352,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * d; idx += ATT_THREADS) {
+    for (int idx = threadIdx.x; idx < G * d; idx += DEC_THREADS) {
         const int row = idx / d, col = idx - row * d;
         float mm = -INFINITY;
 #pragma unroll
@@ -300,7 +389,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int idx = threadIdx.x; idx < G * d; idx += ATT_THREADS) {
+    for (int idx = threadIdx.x; idx < G * d; idx += DEC_THREADS) {
         const int row = idx / d, col = idx - row * d;
         const size_t th = (size_t)tok * p.n_heads + kvh * G + row;
         const float* ml = p.part_ml + th * p.n_splits * 2;
@@ -317,34 +406,29 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(DecodeParams d
     }
 }
 
-// keys per warp tile and stages per warp, by head size: as much in flight as shared memory holds
-template <int DMAX> struct DecodeTiling { static constexpr int BNW = 32, WST = 3; };
-template <> struct DecodeTiling<256> { static constexpr int BNW = 16, WST = 3; };
-
-template <int DMAX> static size_t decode_smem() {
-    using T = DecodeTiling<DMAX>;
-    size_t tiles = (size_t)(16 + 4 * T::WST * 2 * T::BNW) * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
-    size_t merge = (size_t)16 * (DMAX + 8) * 2 + (size_t)(4 * 16 * DMAX + 128) * 4;
+template <int DMAX, bool BULK> static size_t decode_smem() {
+    using T = DecodeTiling<DMAX, BULK>;
+    size_t tiles = (size_t)T::STAGES * T::STAGE_ELEMS * 2 + (size_t)16 * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
+    size_t merge = (size_t)(4 * 16 * DMAX + 128) * 4;
     return tiles > merge ? tiles : merge;
 }
 
-template <int DMAX>
+template <int DMAX, bool BULK>
 static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
     static bool configured = false;
-    size_t smem = decode_smem<DMAX>();
+    size_t smem = decode_smem<DMAX, BULK>();
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DMAX, DecodeTiling<DMAX>::BNW, DecodeTiling<DMAX>::WST>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DMAX, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return pb_fail("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    pb_launch(attn_decode_kernel<DMAX, DecodeTiling<DMAX>::BNW, DecodeTiling<DMAX>::WST>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(ATT_THREADS), smem, stream, dp);
+    pb_launch(attn_decode_kernel<DMAX, BULK>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(DEC_THREADS), smem, stream, dp);
     return 0;
 }
 
 // Blocks of this kernel that one multiprocessor holds at a time (for choosing the number of splits).
 PB_API int pb_attention_decode_blocks_per_sm(int head_dim) {
-    size_t smem = head_dim <= 64 ? decode_smem<64>() : head_dim <= 128 ? decode_smem<128>() : decode_smem<256>();
+    size_t smem = head_dim <= 64 ? decode_smem<64, false>() : head_dim <= 128 ? decode_smem<128, false>() : decode_smem<256, false>();
     int n = (int)((227 * 1024) / (smem + 1024));
     return n < 1 ? 1 : n;
 }
@@ -361,16 +445,17 @@ PB_API long long pb_attention_decode_scratch_floats(int n_tokens, int n_heads, i
 PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                     const int32_t* block_table, int table_stride, const int32_t* positions,
                                     const int32_t* token_seq, int page_size, int num_pages, int n_tokens,
-                                    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int n_splits,
-                                    float* scratch, int* counters, int* status, cudaStream_t stream) {
+                                    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int swizzle,
+                                    int n_splits, float* scratch, int* counters, int* status, cudaStream_t stream) {
     DecodeParams dp{};
     AttnParams& p = dp.a;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.positions = positions; p.token_seq = token_seq;
     p.n_splits = n_splits; p.table_stride = table_stride; p.page_size = page_size; p.num_pages = num_pages;
     p.n_tokens = n_tokens; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window;
-    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.swizzle = swizzle;
     if (int e = attn_check_common("attention_decode", p)) return e;
+    PB_REQUIRE(!swizzle || head_dim % 64 == 0, "attention_decode: permuted pages need head_dim %% 64 == 0");
     p.group = n_heads / n_kv_heads;
     PB_REQUIRE(p.group <= 16, "attention_decode: %d query heads per key/value head; at most 16 fit a tile", p.group);
     PB_REQUIRE(n_splits >= 1 && n_splits <= 1024, "attention_decode: n_splits=%d", n_splits);
@@ -386,8 +471,11 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
     dp.page_shift = -1;
     for (int s = 0; s < 31; ++s)
         if ((1 << s) == page_size) dp.page_shift = s;
-    int e = head_dim <= 64 ? launch_decode<64>(dp, stream)
-          : head_dim <= 128 ? launch_decode<128>(dp, stream) : launch_decode<256>(dp, stream);
+    const bool bulk = swizzle && page_size % 8 == 0;    // the rows of a tile then sit at the row numbers their permutation was made for
+    int e = bulk ? (head_dim <= 64 ? launch_decode<64, true>(dp, stream)
+                    : head_dim <= 128 ? launch_decode<128, true>(dp, stream) : launch_decode<256, true>(dp, stream))
+                 : (head_dim <= 64 ? launch_decode<64, false>(dp, stream)
+                    : head_dim <= 128 ? launch_decode<128, false>(dp, stream) : launch_decode<256, false>(dp, stream));
     if (e) return e;
     PB_CHECK_LAUNCH("attention_decode");
     return 0;

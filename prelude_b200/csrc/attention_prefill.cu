@@ -211,14 +211,14 @@ PB_API int pb_attention_prefill_bf16(const void* q, const void* k_pages, const v
                                      const int32_t* token_seq, const int32_t* cu_q, const int32_t* q_start,
                                      const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size,
                                      int num_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                     float scale, int window, int* status, cudaStream_t stream) {
+                                     float scale, int window, int swizzle, int* status, cudaStream_t stream) {
     AttnParams p{};
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.positions = positions; p.token_seq = token_seq;
     p.cu_q = cu_q; p.q_start = q_start; p.tile_seq = tile_seq; p.tile_tok0 = tile_tok0; p.n_splits = 1;
     p.table_stride = table_stride; p.page_size = page_size; p.num_pages = num_pages; p.n_tokens = n_tokens;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window;
-    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.swizzle = swizzle;
     if (int e = attn_check_common("attention_prefill", p)) return e;
     p.group = n_heads / n_kv_heads;
     PB_REQUIRE(p.group <= 64, "attention_prefill: %d query heads per key/value head; at most 64 fit a tile", p.group);

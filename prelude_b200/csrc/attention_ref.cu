@@ -26,7 +26,7 @@ __global__ void paged_attention_warp_kernel(
     const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages, T* __restrict__ out,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages, int n_tokens,
-    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int* __restrict__ status) {
+    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int swizzle, int* __restrict__ status) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float q_s[ATTN_REF_WARPS][ATTN_REF_MAX_D];
@@ -60,10 +60,11 @@ __global__ void paged_attention_warp_kernel(
             if (page < 0 || page >= num_pages) {
                 bad = true;
             } else {
-                slot = page * page_size + j % page_size;
-                const T* kr = k_pages + ((size_t)slot * n_kv_heads + kvh) * head_dim;
+                slot = (page * n_kv_heads + kvh) * page_size + j % page_size;    // row of this head's run in the page
+                const T* kr = k_pages + (size_t)slot * head_dim;
                 float acc = 0.f;
-                for (int d = 0; d < head_dim; ++d) acc = fmaf(q_s[warp][d], pb_ld(kr + d), acc);
+                const int in_page = j % page_size;
+                for (int d = 0; d < head_dim; ++d) acc = fmaf(q_s[warp][d], pb_ld(kr + pb_kv_elem_offset(d, in_page, swizzle)), acc);
                 s = acc * scale;
             }
         }
@@ -80,11 +81,12 @@ __global__ void paged_attention_warp_kernel(
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int sj = __shfl_sync(0xffffffffu, slot, jj);
             if (sj < 0) continue;
-            const T* vr = v_pages + ((size_t)sj * n_kv_heads + kvh) * head_dim;
+            const T* vr = v_pages + (size_t)sj * head_dim;
+            const int vin = (base + jj) % page_size;
 #pragma unroll
             for (int i = 0; i < ATTN_REF_MAX_D / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < head_dim) o[i] = fmaf(pj, pb_ld(vr + d), o[i]);
+                if (d < head_dim) o[i] = fmaf(pj, pb_ld(vr + pb_kv_elem_offset(d, vin, swizzle)), o[i]);
             }
         }
         m = m_new;
@@ -99,12 +101,12 @@ __global__ void paged_attention_warp_kernel(
     }
 }
 
-// q, out: [n_tokens, n_heads, head_dim]; pages: [num_pages, page_size, n_kv_heads, head_dim];
+// q, out: [n_tokens, n_heads, head_dim]; pages: [num_pages, n_kv_heads, page_size, head_dim];
 // positions, token_seq: [n_tokens]; block_table: [n_seqs, table_stride]; window <= 0: all keys.
 PB_API int pb_paged_attention_ref(const void* q, const void* k_pages, const void* v_pages, void* out, int dtype,
                                   const int32_t* positions, const int32_t* token_seq, const int32_t* block_table,
                                   int table_stride, int page_size, int num_pages, int n_tokens, int n_heads,
-                                  int n_kv_heads, int head_dim, float scale, int window, int* status,
+                                  int n_kv_heads, int head_dim, float scale, int window, int swizzle, int* status,
                                   cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "paged_attention_ref: %d query heads over %d key/value heads", n_heads, n_kv_heads);
@@ -118,7 +120,7 @@ PB_API int pb_paged_attention_ref(const void* q, const void* k_pages, const void
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(paged_attention_warp_kernel<T>, dim3((unsigned)blocks), dim3(ATTN_REF_WARPS * 32), 0, stream, 
             (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, positions, token_seq, block_table,
-            table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, status)));
+            table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, swizzle, status)));
     PB_CHECK_LAUNCH("paged_attention_ref");
     return 0;
 }

@@ -85,6 +85,21 @@ static inline cudaError_t pb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---------------------------------------------------------------------------
+// Layout of a key/value page: [pages, kv heads, page_size tokens, head_dim].
+// One head's tokens of one page are one contiguous run, so an attention kernel
+// fetches them with a single bulk copy.  When `swizzle` is set (bfloat16 pages
+// with head_dim % 64 == 0), the 16-byte chunks of every token row are stored
+// permuted: chunk c of the row of token r lives at chunk position c ^ (r & 7).
+// Copied as they are into shared memory, eight consecutive rows then put any
+// one logical chunk into eight different bank groups, so the tensor-core loads
+// (ldmatrix) are free of bank conflicts without padding.  elem_per_chunk is 8
+// for bfloat16.  Everyone who touches a page goes through this function.
+// ---------------------------------------------------------------------------
+__host__ __device__ __forceinline__ int pb_kv_elem_offset(int elem, int token_in_page, int swizzle) {
+    return swizzle ? ((((elem >> 3) ^ (token_in_page & 7)) << 3) | (elem & 7)) : elem;
+}
+
 // Dispatch a launcher body on an element type code.
 #define PB_DISPATCH_DTYPE(code, T, ...)                              \
     do {                                                             \

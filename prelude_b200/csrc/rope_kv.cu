@@ -2,8 +2,8 @@
 //
 // For every token t and head h of the projected q, k and v rows:
 //   q' = rope(rmsnorm_D(q) * wq, pos_t)   -> q_out[t, h, :]
-//   k' = rope(rmsnorm_D(k) * wk, pos_t)   -> k_pages[page, pos % page_size, h, :]
-//   v                                      -> v_pages[page, pos % page_size, h, :]
+//   k' = rope(rmsnorm_D(k) * wk, pos_t)   -> k_pages[page, h, pos % page_size, :]
+//   v                                      -> v_pages[page, h, pos % page_size, :]
 // with page = block_table[seq_t, pos / page_size].  Norm and rotation are in
 // float32 with one rounding at the end, like the reference's fused kernels
 // (crates/prelude-cuda/src/kernels/kernels_src/rope/qknorm_rope.cu:49-90,
@@ -27,7 +27,7 @@ __global__ void qknorm_rope_kvwrite_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int max_positions,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
-    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv, int* __restrict__ status) {
+    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv, int swizzle, int* __restrict__ status) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     const int heads_per_token = n_heads + (write_kv ? 2 * n_kv_heads : 0);
@@ -42,6 +42,7 @@ __global__ void qknorm_rope_kvwrite_kernel(
     T* dst;
     const float* weight;
     bool rotate;
+    int swz = 0, in_page = 0;           // page rows may be stored with permuted 16-byte chunks
     if (slot < n_heads) {
         src = q + (size_t)t * token_stride + (size_t)slot * head_dim;
         dst = q_out + ((size_t)t * n_heads + slot) * head_dim;
@@ -56,13 +57,15 @@ __global__ void qknorm_rope_kvwrite_kernel(
             if (lane == 0 && status) atomicExch(status, 2);
             return;
         }
-        const size_t row = (((size_t)page * page_size + pos % page_size) * n_kv_heads + h) * head_dim;
+        in_page = pos % page_size;
+        swz = swizzle;
+        const size_t row = (((size_t)page * n_kv_heads + h) * page_size + in_page) * head_dim;
         src = (is_k ? k : v) + (size_t)t * token_stride + (size_t)h * head_dim;
         dst = (is_k ? k_pages : v_pages) + row;
         weight = is_k ? k_weight : nullptr;
         rotate = is_k;
         if (!is_k) {   // values: plain copy
-            for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+            for (int i = lane; i < head_dim; i += 32) dst[pb_kv_elem_offset(i, in_page, swz)] = src[i];
             return;
         }
     }
@@ -87,13 +90,13 @@ __global__ void qknorm_rope_kvwrite_kernel(
         float a = pb_ld(src + j) * inv, b = pb_ld(src + j + half) * inv;
         if (weight != nullptr) { a *= weight[j]; b *= weight[j + half]; }
         float c = cos_table[(size_t)pos * half + j], s = sin_table[(size_t)pos * half + j];
-        pb_st(dst + j, a * c - b * s);
-        pb_st(dst + j + half, b * c + a * s);
+        pb_st(dst + pb_kv_elem_offset(j, in_page, swz), a * c - b * s);
+        pb_st(dst + pb_kv_elem_offset(j + half, in_page, swz), b * c + a * s);
     }
     for (int i = 2 * half + lane; i < head_dim; i += 32) {
         float a = pb_ld(src + i) * inv;
         if (weight != nullptr) a *= weight[i];
-        pb_st(dst + i, a);
+        pb_st(dst + pb_kv_elem_offset(i, in_page, swz), a);
     }
 }
 
@@ -102,11 +105,12 @@ PB_API int pb_qknorm_rope_kvwrite(
     int dtype, const float* q_weight, const float* k_weight, float eps, const float* cos_table,
     const float* sin_table, int rotary_dim, int max_positions, const int32_t* positions, const int32_t* token_seq,
     const int32_t* block_table, int table_stride, int page_size, int num_pages, int n_tokens, int n_heads,
-    int n_kv_heads, int head_dim, int write_kv, int* status, cudaStream_t stream) {
+    int n_kv_heads, int head_dim, int write_kv, int swizzle, int* status, cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0, "qknorm_rope_kvwrite: bad sizes");
     PB_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
                "qknorm_rope_kvwrite: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, head_dim);
     PB_REQUIRE(q && q_out && positions, "qknorm_rope_kvwrite: null pointer");
+    PB_REQUIRE(!swizzle || (dtype == PB_BF16 && head_dim % 64 == 0), "qknorm_rope_kvwrite: permuted pages are bfloat16 with head_dim %% 64 == 0");
     if (write_kv)
         PB_REQUIRE(k && v && k_pages && v_pages && token_seq && block_table && page_size > 0 && num_pages > 0,
                    "qknorm_rope_kvwrite: cache write asked for without cache arguments");
@@ -119,7 +123,7 @@ PB_API int pb_qknorm_rope_kvwrite(
         (pb_launch(qknorm_rope_kvwrite_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream, 
             (const T*)q, (const T*)k, (const T*)v, token_stride, (T*)q_out, (T*)k_pages, (T*)v_pages, q_weight,
             k_weight, eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq, block_table,
-            table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, write_kv, status)));
+            table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, write_kv, swizzle, status)));
     PB_CHECK_LAUNCH("qknorm_rope_kvwrite");
     return 0;
 }

@@ -32,7 +32,7 @@ class LayerCache:
     group, or per-request state, or nothing."""
     kind: Optional[str] = None          # "kv" | "state" | None
     group: int = -1
-    k_pages: Optional[torch.Tensor] = None     # [num_pages, page_size, n_kv_heads, head_dim]
+    k_pages: Optional[torch.Tensor] = None     # [num_pages, n_kv_heads, page_size, head_dim]
     v_pages: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None       # [max_slots, *shape]
 

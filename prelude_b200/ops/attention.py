@@ -71,9 +71,11 @@ def _prefill_plan(batch, group: int):
     return plan
 
 
-def tensor_core_shape_ok(n_heads: int, n_kv_heads: int, head_dim: int, decode: bool) -> bool:
+def tensor_core_shape_ok(n_heads: int, n_kv_heads: int, head_dim: int, decode: bool, page_size: int = 16) -> bool:
     group = n_heads // n_kv_heads
-    return head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= (16 if decode else 64)
+    if not (head_dim % 16 == 0 and 16 <= head_dim <= 256):
+        return False
+    return group <= (16 if decode else 64)
 
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, group: int,
@@ -81,8 +83,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     """q [T, nH, D] of the batch's tokens against the pages of cache group ``group``."""
     table = batch.block_tables[group]
     T, nH, D = q.shape
-    num_pages, page_size, nKV, _ = k_pages.shape
-    if q.dtype != torch.bfloat16 or not tensor_core_shape_ok(nH, nKV, D, batch.decode_only):
+    num_pages, nKV, page_size, _ = k_pages.shape
+    if q.dtype != torch.bfloat16 or not tensor_core_shape_ok(nH, nKV, D, batch.decode_only, page_size):
         return K.paged_attention_ref(q, k_pages, v_pages, batch.positions, batch.token_seq, table, scale, window,
                                      batch.status)
     out = torch.empty_like(q)
@@ -102,7 +104,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         check(lib.pb_attention_decode_bf16(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
             batch.positions.data_ptr(), batch.token_seq.data_ptr(), page_size, num_pages, T, nH, nKV, D, float(scale),
-            win, splits, None if scratch is None else scratch.data_ptr(),
+            win, 1 if K.kv_swizzled(q.dtype, D) else 0, splits, None if scratch is None else scratch.data_ptr(),
             None if counters is None else counters.data_ptr(), batch.status.data_ptr(), stream),
             "attention_decode")
         return out
@@ -111,5 +113,5 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
         batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
         tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
-        batch.status.data_ptr(), stream), "attention_prefill")
+        1 if K.kv_swizzled(q.dtype, D) else 0, batch.status.data_ptr(), stream), "attention_prefill")
     return out

@@ -33,6 +33,14 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def kv_swizzled(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether key/value pages of this type and head size store the 16-byte chunks
+    of a token row permuted (chunk c of token r at position c ^ (r & 7)).  The rule
+    is a function of the page tensor alone, so the kernel that writes a page and
+    the kernels that read it always agree."""
+    return dtype == torch.bfloat16 and head_dim % 64 == 0
+
+
 def _need(t: torch.Tensor, name: str, dtype=None, contiguous=True) -> None:
     if not t.is_cuda:
         raise KernelLibraryError(f"{name} must live on a CUDA device")
@@ -112,7 +120,7 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
     """q/k norm + rotation, q to a dense [T, nH, D] tensor, k and v into their pages.
 
     ``qkv`` is the merged projection [T, (nH + 2 nKV) D] (or [T, nH D] when
-    nothing is written).  Pages are [num_pages, page_size, nKV, D].
+    nothing is written).  Pages are [num_pages, nKV, page_size, D].
     """
     _need(qkv, "qkv", contiguous=False)
     if qkv.dim() != 2 or qkv.stride(1) != 1:
@@ -137,8 +145,8 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
         _need(v_pages, "v_pages", qkv.dtype)
         _need(block_table, "block_table", torch.int32)
         _need(token_seq, "token_seq", torch.int32)
-        num_pages, page_size = k_pages.shape[0], k_pages.shape[1]
-        if tuple(k_pages.shape[2:]) != (n_kv_heads, head_dim) or k_pages.shape != v_pages.shape:
+        num_pages, page_size = k_pages.shape[0], k_pages.shape[2]
+        if (k_pages.shape[1], k_pages.shape[3]) != (n_kv_heads, head_dim) or k_pages.shape != v_pages.shape:
             raise KernelLibraryError(f"qknorm_rope_kvwrite: pages {tuple(k_pages.shape)} do not fit "
                                      f"{n_kv_heads} heads of {head_dim}")
         stride = block_table.shape[1]
@@ -153,7 +161,8 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
         _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, dtype_code(qkv.dtype),
         _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
         max_pos, positions.data_ptr(), _ptr(token_seq), _ptr(block_table), stride, page_size, num_pages, T, n_heads,
-        n_kv_heads, head_dim, 1 if write_kv else 0, _ptr(status), _stream()), "qknorm_rope_kvwrite")
+        n_kv_heads, head_dim, 1 if write_kv else 0, 1 if (write_kv and kv_swizzled(qkv.dtype, head_dim)) else 0,
+        _ptr(status), _stream()), "qknorm_rope_kvwrite")
     return q_out
 
 
@@ -168,15 +177,15 @@ def paged_attention_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     _need(token_seq, "token_seq", torch.int32)
     _need(block_table, "block_table", torch.int32)
     T, nH, D = q.shape
-    num_pages, page_size, nKV, Dk = k_pages.shape
+    num_pages, nKV, page_size, Dk = k_pages.shape
     if Dk != D or v_pages.shape != k_pages.shape:
         raise KernelLibraryError("paged_attention_ref: q and pages disagree on the head size")
     out = torch.empty_like(q)
     check(_l.library().pb_paged_attention_ref(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
         positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
-        num_pages, T, nH, nKV, D, float(scale), int(window) if window else 0, _ptr(status), _stream()),
-        "paged_attention_ref")
+        num_pages, T, nH, nKV, D, float(scale), int(window) if window else 0, 1 if kv_swizzled(q.dtype, D) else 0,
+        _ptr(status), _stream()), "paged_attention_ref")
     return out
 
 

@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class KernelLibraryError(RuntimeError):
@@ -30,8 +30,8 @@ _SIGNATURES = {
     "pb_add_rmsnorm": ([P, P, P, P, I, I, I, F, P], I),
     "pb_rmsnorm": ([P, P, P, I, I, I, F, P], I),
     "pb_gather_add_rmsnorm": ([P, P, P, P, P, I, I, I, I, F, P], I),
-    "pb_qknorm_rope_kvwrite": ([P, P, P, L, P, P, P, I, P, P, F, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P, P], I),
-    "pb_paged_attention_ref": ([P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P], I),
+    "pb_qknorm_rope_kvwrite": ([P, P, P, L, P, P, P, I, P, P, F, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, I, P, P], I),
+    "pb_paged_attention_ref": ([P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
     "pb_silu_mul": ([P, P, I, I, I, P], I),
     "pb_gemm_ref": ([P, P, P, P, I, I, I, I, I, L, L, L, P], I),
     "pb_sample_scratch_floats": ([I, I], L),
@@ -39,10 +39,10 @@ _SIGNATURES = {
     "pb_sample": ([P, L, I, I, P, P, P, P, P, P], I),
     "pb_softmax_temperature": ([P, L, I, I, P, P, P], I),
     "pb_philox_uniform": ([c_uint64, c_uint64], F),
-    "pb_attention_prefill_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P], I),
+    "pb_attention_prefill_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
     "pb_attention_decode_scratch_floats": ([I, I, I, I], L),
     "pb_attention_decode_blocks_per_sm": ([I], I),
-    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P], I),
+    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P], I),
     "pb_gemm_skinny_scratch_bytes": ([I, I, I], L),
     "pb_gemm_skinny_supported": ([I, I, I, L, L], I),
     "pb_gemm_skinny_bf16": ([P, P, P, P, I, I, I, L, L, L, P, P], I),

@@ -92,17 +92,54 @@ def test_gemm_ref(dtype, M, N, K_):
     assert torch.equal(K().gemm_ref(wide[:, 8:8 + K_], w), K().gemm_ref(wide[:, 8:8 + K_].contiguous(), w))
 
 
+def _stored(rows, dtype):
+    """A run of token rows [..., page_size, D] as the page layout stores it: for bfloat16
+    pages with D % 64 == 0 the 16-byte chunks of token r are permuted, chunk c sits at c ^ (r & 7)."""
+    D, ps = rows.shape[-1], rows.shape[-2]
+    if not (dtype == torch.bfloat16 and D % 64 == 0):
+        return rows
+    chunks = rows.reshape(*rows.shape[:-1], D // 8, 8)
+    out = torch.empty_like(chunks)
+    for r in range(ps):
+        for c in range(D // 8):
+            out[..., r, c ^ (r & 7), :] = chunks[..., r, c, :]
+    return out.reshape(rows.shape)
+
+
+def _put(pages_tensor, page, in_page, row):
+    """Write one token's [nKV, D] row into its page at the stored position of every chunk."""
+    D = row.shape[-1]
+    if pages_tensor.dtype == torch.bfloat16 and D % 64 == 0:
+        ch = row.reshape(row.shape[0], D // 8, 8)
+        perm = torch.tensor([c ^ (in_page & 7) for c in range(D // 8)])
+        stored = torch.empty_like(ch)
+        stored[:, perm] = ch
+        pages_tensor[page, :, in_page] = stored.reshape(row.shape)
+    else:
+        pages_tensor[page, :, in_page] = row
+
+
+def _get(pages_tensor, page, in_page):
+    D = pages_tensor.shape[-1]
+    row = pages_tensor[page, :, in_page]
+    if pages_tensor.dtype == torch.bfloat16 and D % 64 == 0:
+        ch = row.reshape(row.shape[0], D // 8, 8)
+        perm = torch.tensor([c ^ (in_page & 7) for c in range(D // 8)])
+        return ch[:, perm].reshape(row.shape)
+    return row
+
+
 def _paged(k, v, page_size, num_pages, seed):
     """Scatter dense [L, nKV, D] keys and values into randomly chosen pages."""
     L = k.shape[0]
     n = -(-L // page_size)
     g = torch.Generator().manual_seed(seed)
     pages = torch.randperm(num_pages, generator=g)[:n].tolist()
-    kp = torch.full((num_pages, page_size) + tuple(k.shape[1:]), float("nan"), dtype=k.dtype, device=DEV)
+    kp = torch.full((num_pages, k.shape[1], page_size, k.shape[2]), float("nan"), dtype=k.dtype, device=DEV)
     vp = torch.full_like(kp, float("nan"))
     for i in range(L):
-        kp[pages[i // page_size], i % page_size] = k[i]
-        vp[pages[i // page_size], i % page_size] = v[i]
+        _put(kp, pages[i // page_size], i % page_size, k[i])
+        _put(vp, pages[i // page_size], i % page_size, v[i])
     return kp, vp, pages
 
 
@@ -182,7 +219,7 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
     positions = torch.tensor([3, 4, 5, 6, 7, 8, 9, 0, 1, 2, 3], dtype=torch.int32, device=DEV)
     seq = torch.tensor([1] * 7 + [0] * 4, dtype=torch.int32, device=DEV)
     table = torch.tensor([[4, -1], [7, 2]], dtype=torch.int32, device=DEV)
-    kp = torch.zeros(num_pages, page, nKV, D, dtype=dtype, device=DEV)
+    kp = torch.zeros(num_pages, nKV, page, D, dtype=dtype, device=DEV)
     vp = torch.zeros_like(kp)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     q_out = K().qknorm_rope_kvwrite(qkv, nH, nKV, D, qw, kw, eps, cos, sin, rot, positions, seq, table, kp, vp, True, status)
@@ -206,10 +243,11 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
     for t in range(T):
         p, r = int(positions[t]), int(seq[t])
         pg = int(table[r, p // page])
-        assert (kp[pg, p % page].float() - want_k[t]).abs().max() <= tol(dtype, 4.0)
-        assert torch.equal(vp[pg, p % page], v[t])
+        assert (_get(kp, pg, p % page).float() - want_k[t]).abs().max() <= tol(dtype, 4.0)
+        assert torch.equal(_get(vp, pg, p % page), v[t])
         written[pg, p % page] = True
-    assert float(kp[~written.to(DEV)].abs().max()) == 0 and float(vp[~written.to(DEV)].abs().max()) == 0
+    unwritten = ~written.to(DEV)[:, None, :].expand(-1, nKV, -1)
+    assert float(kp[unwritten].abs().max()) == 0 and float(vp[unwritten].abs().max()) == 0
     # q only (a layer that reads another layer's cache)
     q_only = K().qknorm_rope_kvwrite(qkv[:, :nH * D], nH, nKV, D, qw, kw, eps, cos, sin, rot, positions, None, None,
                                      None, None, False)
@@ -224,14 +262,14 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
 def test_kernels_refuse_what_they_cannot_do():
     from prelude_b200.ops.library import KernelLibraryError
     q = rnd(1, 2, 272)
-    kp = torch.zeros(2, 4, 2, 272, device=DEV)
+    kp = torch.zeros(2, 2, 4, 272, device=DEV)
     one = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(KernelLibraryError, match="head_dim"):
         K().paged_attention_ref(q, kp, kp, one, one, torch.zeros(1, 1, dtype=torch.int32, device=DEV), 1.0)
     with pytest.raises(KernelLibraryError, match="rotary_dim"):
         K().qknorm_rope_kvwrite(rnd(1, 64), 2, 1, 16, None, None, 0.0, torch.zeros(4, 9, device=DEV),
                                 torch.zeros(4, 9, device=DEV), 18, one, one, torch.zeros(1, 1, dtype=torch.int32, device=DEV),
-                                torch.zeros(1, 4, 1, 16, device=DEV), torch.zeros(1, 4, 1, 16, device=DEV), True)
+                                torch.zeros(1, 1, 4, 16, device=DEV), torch.zeros(1, 1, 4, 16, device=DEV), True)
     with pytest.raises(KernelLibraryError):
         K().gemm_ref(rnd(2, 3), rnd(4, 5))
     with pytest.raises(KernelLibraryError, match="float32 or bfloat16"):
@@ -319,7 +357,7 @@ def _batch_for(requests, page, num_pages, nKV, D, seed, trimmed_below=None):
     from prelude_b200.engine.batch import StepItem, build_step_batch
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(num_pages, generator=g).tolist()
-    kp = torch.full((num_pages, page, nKV, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kp = torch.full((num_pages, nKV, page, D), float("nan"), dtype=torch.bfloat16, device=DEV)
     vp = torch.full_like(kp, float("nan"))
     ks, vs, tables, items = [], [], [], []
     for i, (ctx, qn) in enumerate(requests):
@@ -327,8 +365,8 @@ def _batch_for(requests, page, num_pages, nKV, D, seed, trimmed_below=None):
         n = -(-ctx // page)
         pages, perm = perm[:n], perm[n:]
         for j in range(ctx):
-            kp[pages[j // page], j % page] = k[j]
-            vp[pages[j // page], j % page] = v[j]
+            _put(kp, pages[j // page], j % page, k[j])
+            _put(vp, pages[j // page], j % page, v[j])
         if trimmed_below is not None:                       # pages wholly below this position have been given back
             pages = [-1 if (pi + 1) * page <= trimmed_below[i] else pg for pi, pg in enumerate(pages)]
         ks.append(k); vs.append(v); tables.append(pages)
@@ -400,7 +438,7 @@ def test_tensor_core_attention_finds_the_one_key_that_matters(monkeypatch, decod
     q[-1] = (unit * 30).to(torch.bfloat16)
     pg = int(batch.block_tables[0][0, target // page])
     kp[:, :, :, :] = (kp.float() * 0.05).to(torch.bfloat16)
-    kp[pg, target % page] = (unit * 30).to(torch.bfloat16)         # score 900 / sqrt(128) = 80 against ~0
+    _put(kp, pg, target % page, (unit * 30).to(torch.bfloat16).expand(nKV, D))      # score 900 / sqrt(128) = 80 against ~0
     use_window = window if where in ("window_first", "just_outside_window") else None
     got = paged_attention(q, kp, vp, batch, 0, 1 / math.sqrt(D), use_window)
     hit = (got[-1, 0].float() - vs[0][target, 0].float()).abs().max() < 0.06
@@ -439,9 +477,11 @@ def test_gemm_skinny(M, N, K_):
     assert torch.equal(gemm_skinny(wide[:, 32:32 + K_], w), gemm_skinny(wide[:, 32:32 + K_].contiguous(), w))
 
 
-def test_gemm_skinny_refuses_other_shapes_and_linear_falls_back():
+def test_gemm_skinny_refuses_other_shapes_and_linear_falls_back(monkeypatch):
+    from prelude_b200.ops import linear as linear_module
     from prelude_b200.ops.library import KernelLibraryError
     from prelude_b200.ops.linear import gemm_skinny, linear, skinny_takes
+    monkeypatch.setattr(linear_module, "SKINNY_MAX_ROWS", 16)
     x, w = rnd(4, 72, dtype=torch.bfloat16), rnd(40, 72, dtype=torch.bfloat16)
     assert not skinny_takes(x, w)
     with pytest.raises(KernelLibraryError, match="not taken"):
