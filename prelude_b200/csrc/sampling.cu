@@ -272,3 +272,53 @@ PB_API int pb_softmax_temperature(const float* logits, long long row_stride, int
     PB_CHECK_LAUNCH("softmax_temperature");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Row-wise argmax that brings its own scratch (declared in no_alloc.h).
+//
+// pb_argmax needs a few floats of scratch per row for its two passes, and its
+// callers get them from an allocator.  Some callers have none to ask: a C or
+// C++ host that links this library without torch and runs with a fixed memory
+// plan, or code that runs where allocation is forbidden (a stream that is being
+// captured, a callback on the launch path).  For them the scratch lives in the
+// library image: one array per GPU, 256 KB, present from the moment the library
+// is loaded on that GPU until the process ends.
+//
+// Nothing in the array has to start at zero: the first pass writes every slot
+// the second pass reads.  All calls share the one array and it keeps what the
+// last call left there, so two calls that run on the GPU at the same time (two
+// streams, two threads) overwrite each other's partial results; calls on one
+// stream are safe.  The first call on a device looks up the array's device
+// address (cudaGetSymbolAddress: no allocation, but it may load the module), so
+// make that first call before any stream capture begins.
+// ---------------------------------------------------------------------------
+#define PB_NOALLOC_MAX_ROWS 256
+#define PB_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_noalloc_scratch[PB_NOALLOC_MAX_ROWS * PART_MAX_BLOCKS * 4];
+static float* g_noalloc_scratch_addr[PB_NOALLOC_MAX_DEVICES] = {nullptr};
+
+PB_API int pb_argmax_noalloc(const float* logits, long long row_stride, int rows, int vocab, int32_t* out,
+                             cudaStream_t stream) {
+    PB_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "argmax_noalloc: bad sizes rows=%d vocab=%d", rows, vocab);
+    PB_REQUIRE(rows <= PB_NOALLOC_MAX_ROWS,
+               "argmax_noalloc: rows=%d is more than the %d rows the built-in scratch holds; split the call or use pb_argmax",
+               rows, PB_NOALLOC_MAX_ROWS);
+    PB_REQUIRE(logits && out, "argmax_noalloc: null pointer");
+    if (rows == 0) return 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return pb_fail("argmax_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    PB_REQUIRE(dev >= 0 && dev < PB_NOALLOC_MAX_DEVICES, "argmax_noalloc: device %d", dev);
+    if (g_noalloc_scratch_addr[dev] == nullptr) {
+        // the array's name is a host-side handle here, not a device address: ask the runtime for the address
+        float* addr = nullptr;
+        e = cudaGetSymbolAddress((void**)&addr, g_noalloc_scratch);
+        if (e != cudaSuccess || addr == nullptr)
+            return pb_fail("argmax_noalloc: cannot find the built-in scratch on device %d: %s", dev, cudaGetErrorString(e));
+        g_noalloc_scratch_addr[dev] = addr;
+    }
+    launch_two_pass(logits, row_stride, rows, vocab, nullptr, nullptr, nullptr, g_noalloc_scratch_addr[dev], out, stream);
+    PB_CHECK_LAUNCH("argmax_noalloc");
+    return 0;
+}
