@@ -471,7 +471,9 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
     dp.page_shift = -1;
     for (int s = 0; s < 31; ++s)
         if ((1 << s) == page_size) dp.page_shift = s;
-    const bool bulk = swizzle && page_size % 8 == 0;    // the rows of a tile then sit at the row numbers their permutation was made for
+    // bulk copies bring whole runs of a page: a run must tile the 64-key tile evenly and start at a multiple
+    // of 8 tokens (the rows then sit at the row numbers their permutation was made for)
+    const bool bulk = swizzle && page_size % 8 == 0 && (BNW % page_size == 0 || page_size % BNW == 0);
     int e = bulk ? (head_dim <= 64 ? launch_decode<64, true>(dp, stream)
                     : head_dim <= 128 ? launch_decode<128, true>(dp, stream) : launch_decode<256, true>(dp, stream))
                  : (head_dim <= 64 ? launch_decode<64, false>(dp, stream)

@@ -1,9 +1,8 @@
-// Tensor-core paged attention for bfloat16: one kernel for prompt portions, one
-// for decode steps with the key range split over several blocks, and the merge
-// of the splits.
+// Tensor-core paged attention for prompt portions (and any mix of portions and
+// single tokens), bfloat16.
 //
-// Both kernels compute, for a query at absolute position p of request r and
-// query head h (key/value head h / G):
+// For a query at absolute position p of request r and query head h (key/value
+// head h / G):
 //     o = softmax_j( (q . k_j) * scale ) v_j    over  max(0, p - window + 1) <= j <= p
 // with k_j, v_j read from the request's pages through its block table
 // (crates/prelude-core/src/models/qwen3.rs:191-222; the reference hands this to
@@ -12,165 +11,462 @@
 // probabilities are rounded to bfloat16 for the second product, whose
 // accumulator is float32.
 //
-// Layout of the work.  The G query heads that share a key/value head are packed
-// into the rows of the tensor-core tile, so keys and values are read once per
-// group.  Keys and values come through shared memory in tiles of 64 keys,
-// gathered page by page with 16-byte asynchronous copies, double buffered.
-//   prefill: a block owns 64 rows = 64/G tokens x G heads of one request and one
-//            key/value head; each of its 4 warps owns 16 rows and walks all keys.
-//   decode:  a block owns the G rows of one token and one key/value head and a
-//            contiguous share of the key tiles; its 4 warps take 16 keys each of
-//            every tile and are merged at the end.  With more than one split the
-//            block writes an unnormalised partial result (float32) and its
-//            running maximum and sum to scratch memory; a merge kernel adds the
-//            splits up in ascending order.
-// Head sizes: multiples of 16 up to 256 (register arrays are sized for 64, 128
-// or 256).  Row strides in shared memory are padded by 16 bytes so that the
-// 8 x 16-byte rows of an ldmatrix fall into different banks.
+// Layout of the work.  The host lists tiles: a tile is 64 rows = 64/G tokens x
+// the G query heads that share a key/value head, of one request, so keys and
+// values are read once per group.  A block owns one tile and one key/value head;
+// each of its four compute warps owns 16 rows and walks all visible keys in
+// tiles of 64.  Two ways of bringing the key and value tiles into shared memory:
+//   bulk - a fifth warp fetches, per tile, each page's run of one head with a
+//          single bulk copy (cp.async.bulk) into a ring of stages, each with a
+//          full and an empty barrier; the runs are stored with permuted 16-byte
+//          chunks (pb_kv_elem_offset), so they land ready for conflict-free
+//          ldmatrix.  No block-wide barrier in the loop.  Taken when pages are
+//          permuted, head_dim is 64, 128 or 256 and a page's run tiles a
+//          64-key tile evenly.
+//   lsu  - the four warps copy 16 bytes per lane (cp.async) into padded rows,
+//          double buffered, with a block-wide barrier per tile; any head size
+//          (multiples of 16 up to 256) and page size.
+// The inner loops are written for few instructions per tensor-core product:
+// the byte offsets of every ldmatrix are per-thread constants plus immediates,
+// masking runs only in tiles that hold an invisible key, the scale is folded
+// into the exponent's multiply-add, and the accumulator is rescaled only when
+// a row's maximum grew by more than 2^8 (the sum and the accumulator then stay
+// relative to a slightly stale maximum, which the final division cancels).
 #include "attention_common.cuh"
 
-// ---------------------------------------------------------------------------------------
-// prefill: 64 rows (tokens x heads of a group) against all visible keys
-// ---------------------------------------------------------------------------------------
-template <int DMAX>
-__global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnParams p) {
-    pb_grid_dep_launch();
-    pb_grid_dep_wait();
-    constexpr int STRIDE = DMAX + 8;
+#include <type_traits>
+
+#define PF_ROWS 64              // rows of a block's tile
+#define PF_COMPUTE_THREADS 128
+#define PF_RESCALE_STEP 8.0f    // log2 of the growth of a row maximum that forces a rescale
+
+template <int I, int N, typename F> __device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
+
+// ldmatrix from a shared-memory byte address plus a compile-time offset
+template <int IMM> __device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(IMM));
+}
+template <int IMM> __device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(IMM));
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int DMAX, bool BULK> struct PrefillTiling {
+    static constexpr int STRIDE = BULK ? DMAX : DMAX + 8;     // elements per row in shared memory
+    static constexpr int ROW_BYTES = STRIDE * 2;
+    static constexpr int TILE_BYTES = BN * ROW_BYTES;          // one tile of keys (or of values)
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int STAGES = BULK ? (DMAX <= 128 ? 3 : 2) : 2;
+    static constexpr int Q_BYTES = PF_ROWS * ROW_BYTES;
+    static constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES;
+    static constexpr int THREADS = BULK ? PF_COMPUTE_THREADS + 32 : PF_COMPUTE_THREADS;
+    static constexpr int BLOCKS_PER_SM = (2 * (SMEM_BYTES + 1024) <= 227 * 1024) ? 2 : 1;
+    // ldmatrix row addresses: with permuted chunks, chunk c of row r sits at c ^ (r & 7).  The chunk
+    // index of step kk is 2 kk + b with a per-lane bit b, and r & 7 = lane & 7, so the position is
+    // (2 kk) ^ x with the per-lane constant x = b ^ (lane & 7): four distinct values of the low bits
+    // (kk & 3), kept in registers, and bit 3 of the chunk (kk >> 2), an immediate.
+    static constexpr int NOFF = BULK ? 4 : 1;
+};
+
+struct PrefillParams {
+    AttnParams a;
+    int page_shift;             // log2(page_size) when it is a power of two, else -1
+};
+
+// What a compute thread keeps about its place in the fragments.
+template <int DMAX, bool BULK> struct FragOffsets {
+    unsigned q[PrefillTiling<DMAX, BULK>::NOFF], k[PrefillTiling<DMAX, BULK>::NOFF], v[PrefillTiling<DMAX, BULK>::NOFF];
+};
+
+template <int DMAX, bool BULK, int KK> __device__ __forceinline__ constexpr int step_imm() {
+    // byte offset of 16-element step KK beyond the per-lane offset that serves it
+    return BULK ? (KK >> 2) * 128 : KK * 32;
+}
+
+// One 64-key tile against this warp's 16 rows.
+template <int DMAX, bool BULK>
+__device__ __forceinline__ void prefill_tile(float (&o)[DMAX / 8][4], float (&m)[2], float (&l)[2],
+                                             const FragOffsets<DMAX, BULK>& f, unsigned sQ, unsigned sK, unsigned sV,
+                                             int d, int key0, const int (&row_pos)[2], bool edge, int window,
+                                             float scale_log2, int t4) {
+    using T = PrefillTiling<DMAX, BULK>;
     constexpr int KSTEPS = DMAX / 16;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* sKV = sQ + 64 * STRIDE;                 // 2 stages x (K, V) x BN rows
+    constexpr bool PIPE = DMAX <= 128;        // larger heads leave no registers for fragments fetched ahead
 
-    const int G = p.group, d = p.head_dim;
-    const int tpt = 64 / G;                                // tokens per tile
-    const int tile = blockIdx.x, kvh = blockIdx.y;
-    const int r = p.tile_seq[tile], tok0 = p.tile_tok0[tile];
-    const int q_base = p.cu_q[r], q_len = p.cu_q[r + 1] - q_base, pos0 = p.q_start[r];
-    const int n_tok = min(tpt, q_len - tok0);              // tokens of this tile
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const int32_t* table = p.block_table + (size_t)p.token_seq[q_base + tok0] * p.table_stride;
-
-    // Q rows: row i -> token tok0 + i / G, head kvh * G + i % G
+    // ---- S = Q K^T: 16 rows x 64 keys; the fragments of the next 16-element step are fetched ahead ----
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
     {
-        const int chunks = d >> 3;
-        for (int c = threadIdx.x; c < 64 * chunks; c += ATT_THREADS) {
-            const int row = c / chunks, ch = c - row * chunks;
-            const int tl = row / G, hg = row - tl * G;
-            const bool ok = tl < n_tok;
-            const size_t src = ok ? (((size_t)(q_base + tok0 + tl) * p.n_heads + kvh * G + hg) * d + ch * 8) : 0;
-            cp_async16(sQ + row * STRIDE + ch * 8, p.q + src, ok);
-        }
-    }
-    const int p_min = pos0 + tok0, p_max = pos0 + tok0 + n_tok - 1;
-    const int lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
-    const int kt0 = lo / BN, kt1 = p_max / BN;
-    const int kv_end = p_max + 1;
-    load_kv_tile<DMAX>(sKV, sKV + BN * STRIDE, p, table, kvh, kt0 * BN, lo, kv_end);
-    cp_async_commit();
-
-    // this thread's two rows
-    int row_pos[2];
+        unsigned qa[PIPE ? 2 : 1][4], kb[PIPE ? 2 : 1][4][4];
+        unsigned kaddr[T::NOFF], qaddr[T::NOFF];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int row = warp * 16 + g + 8 * h;
-        const int tl = row / G;
-        row_pos[h] = tl < n_tok ? pos0 + tok0 + tl : -1;    // -1: no key is visible
-    }
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[DMAX / 8][4];
-#pragma unroll
-    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-
-    for (int kt = kt0; kt <= kt1; ++kt) {
-        const int stage = (kt - kt0) & 1;
-        __nv_bfloat16* sK = sKV + stage * 2 * BN * STRIDE;
-        __nv_bfloat16* sV = sK + BN * STRIDE;
-        if (kt < kt1) {
-            __nv_bfloat16* nK = sKV + (stage ^ 1) * 2 * BN * STRIDE;
-            load_kv_tile<DMAX>(nK, nK + BN * STRIDE, p, table, kvh, (kt + 1) * BN, lo, kv_end);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-
-        // S = Q K^T : 16 rows x 64 keys per warp
-        float s[8][4];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-            if (kk * 16 < d) {
-                unsigned a[4];
-                ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (warp * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        for (int j = 0; j < T::NOFF; ++j) { kaddr[j] = sK + f.k[j]; qaddr[j] = sQ + f.q[j]; }
+        auto fetch = [&](auto kk_c, int buf) {
+            constexpr int kk = decltype(kk_c)::value;
+            constexpr int imm = step_imm<DMAX, BULK, kk>();
+            ldsm_x4<imm>(qa[buf], qaddr[BULK ? (kk & 3) : 0]);
+            static_for<0, 4>([&](auto n2_c) {
+                constexpr int n2 = decltype(n2_c)::value;
+                ldsm_x4<imm + n2 * 16 * T::ROW_BYTES>(kb[buf][n2], kaddr[BULK ? (kk & 3) : 0]);
+            });
+        };
+        if (PIPE) fetch(std::integral_constant<int, 0>{}, 0);
+        static_for<0, KSTEPS>([&](auto kk_c) {
+            constexpr int kk = decltype(kk_c)::value;
+            constexpr int buf = PIPE ? (kk & 1) : 0;
+            if (BULK || kk * 16 < d) {
+                if constexpr (!PIPE) fetch(kk_c, 0);
+                else if constexpr (kk + 1 < KSTEPS) {
+                    if (BULK || (kk + 1) * 16 < d) fetch(std::integral_constant<int, kk + 1>{}, buf ^ 1);
+                }
 #pragma unroll
                 for (int n2 = 0; n2 < 4; ++n2) {
-                    unsigned b0, b1, b2, b3;
-                    const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
-                    ldmatrix_x4(b0, b1, b2, b3, sK + key * STRIDE + col);
-                    mma_bf16(s[2 * n2], a, b0, b1);
-                    mma_bf16(s[2 * n2 + 1], a, b2, b3);
+                    mma_bf16_free(s[2 * n2], qa[buf], kb[buf][n2][0], kb[buf][n2][1]);
+                    mma_bf16_free(s[2 * n2 + 1], qa[buf], kb[buf][n2][2], kb[buf][n2][3]);
                 }
             }
-        }
-        // mask, running maximum and sum
-        float rmax[2] = {-INFINITY, -INFINITY};
+        });
+    }
+
+    // ---- mask (only in tiles with an invisible key), running maximum ----
+    if (edge) {
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = kt * BN + nt * 8 + 2 * t4 + (e & 1);
+                const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
                 const int pr = row_pos[e >> 1];
-                const bool vis = j <= pr && (p.window <= 0 || j > pr - p.window);
-                const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+                const bool vis = j <= pr && (window <= 0 || j > pr - window);
+                s[nt][e] = vis ? s[nt][e] : -INFINITY;
             }
         }
-        float corr[2], mref[2];
+    }
+    float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+        rmax[0] = fmaxf(rmax[0], fmaxf(s[nt][0], s[nt][1]));
+        rmax[1] = fmaxf(rmax[1], fmaxf(s[nt][2], s[nt][3]));
+    }
+    bool grow = false;
+    float cand[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
+        rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
+        cand[h] = fmaxf(m[h], rmax[h] * scale_log2);          // scale > 0: the maximum commutes with it
+        grow = grow || cand[h] > m[h] + PF_RESCALE_STEP;      // also true for -inf -> finite
+    }
+    if (__any_sync(0xffffffffu, grow)) {
+        float corr[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
-            rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
-            const float m_new = fmaxf(m[h], rmax[h]);
-            corr[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);
-            mref[h] = (m_new == -INFINITY) ? 0.f : m_new;   // exp2f(-inf - 0) = 0 for rows that see nothing yet
-            m[h] = m_new;
+            corr[h] = (m[h] == -INFINITY) ? 0.f : ex2_approx(m[h] - cand[h]);   // cand >= m; both -inf: nothing summed yet
+            m[h] = cand[h];
             l[h] *= corr[h];
-        }
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float pv = exp2f(s[nt][e] - mref[e >> 1]);
-                s[nt][e] = pv;
-                l[e >> 1] += pv;
-            }
         }
 #pragma unroll
         for (int i = 0; i < DMAX / 8; ++i) {
             o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
-        // O += P V
+    }
+    // exp2(s * scale - m); a row that has seen nothing yet has m = -inf and only -inf scores: exp2(-inf - 0) = 0
+    const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pv = ex2_approx(fmaf(s[nt][e], scale_log2, -mref[e >> 1]));
+            s[nt][e] = pv;
+            l[e >> 1] += pv;
+        }
+    }
+
+    // ---- O += P V: 4 key steps x KSTEPS dim steps, one ldmatrix and two products each, fetched two steps ahead ----
+    {
+        unsigned pa[4][4];
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-            unsigned a[4] = {pack_bf16(s[2 * ks][0], s[2 * ks][1]), pack_bf16(s[2 * ks][2], s[2 * ks][3]),
-                             pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]), pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+            pa[ks][0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+            pa[ks][1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+            pa[ks][2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+            pa[ks][3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+        }
+        unsigned vaddr[T::NOFF];
 #pragma unroll
-            for (int d2 = 0; d2 < KSTEPS; ++d2) {
-                if (d2 * 16 < d) {
-                    unsigned b0, b1, b2, b3;
-                    const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
-                    ldmatrix_x4_trans(b0, b1, b2, b3, sV + key * STRIDE + col);
-                    mma_bf16(o[2 * d2], a, b0, b1);
-                    mma_bf16(o[2 * d2 + 1], a, b2, b3);
-                }
+        for (int j = 0; j < T::NOFF; ++j) vaddr[j] = sV + f.v[j];
+        constexpr int TOTAL = 4 * KSTEPS, AHEAD = PIPE ? 2 : 0;
+        unsigned vb[PIPE ? 3 : 1][4];
+        auto fetch_v = [&](auto t_c) {
+            constexpr int t = decltype(t_c)::value;
+            constexpr int ks = t / KSTEPS, d2 = t % KSTEPS;
+            if (BULK || d2 * 16 < d)
+                ldsm_x4_trans<step_imm<DMAX, BULK, d2>() + ks * 16 * T::ROW_BYTES>(vb[PIPE ? t % 3 : 0], vaddr[BULK ? (d2 & 3) : 0]);
+        };
+        static_for<0, AHEAD>([&](auto t_c) { fetch_v(t_c); });
+        static_for<0, TOTAL>([&](auto t_c) {
+            constexpr int t = decltype(t_c)::value;
+            constexpr int ks = t / KSTEPS, d2 = t % KSTEPS;
+            if constexpr (t + AHEAD < TOTAL || AHEAD == 0) fetch_v(std::integral_constant<int, t + AHEAD>{});
+            if (BULK || d2 * 16 < d) {
+                constexpr int b = PIPE ? t % 3 : 0;
+                mma_bf16_free(o[2 * d2], pa[ks], vb[b][0], vb[b][1]);
+                mma_bf16_free(o[2 * d2 + 1], pa[ks], vb[b][2], vb[b][3]);
+            }
+        });
+    }
+}
+
+__device__ __forceinline__ void pf_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Keys and values of one tile through the load/store path: thread `tid` of 128 copies 16-byte chunk
+// `ch` of rows row0, row0 + rows_per_pass, ...; rows outside [kv_begin, kv_end) are zero-filled.
+// Pages below kv_begin may have been given back already and are never looked up.
+template <int DMAX>
+__device__ __forceinline__ void load_kv_tile_lsu(unsigned char* sK, unsigned char* sV, const AttnParams& p,
+                                                 const int32_t* table, int kvh, int key0, int kv_begin, int kv_end,
+                                                 int row0, int ch, int rows_per_pass) {
+    constexpr int ROW_BYTES = (DMAX + 8) * 2;
+    if (row0 >= rows_per_pass) return;                     // threads beyond the last whole row of a pass
+    const int ps = p.page_size, d = p.head_dim;
+    int j = key0 + row0;
+    int pi = j / ps, in_page = j - pi * ps;
+    for (int row = row0; row < BN; row += rows_per_pass) {
+        bool ok = j >= kv_begin && j < kv_end;
+        size_t src = 0;
+        if (ok) {
+            const int page = table[pi];
+            if (page < 0 || page >= p.num_pages) {
+                ok = false;
+                if (p.status) atomicExch(p.status, 6);
+            } else {
+                src = (((size_t)page * p.n_kv_heads + kvh) * ps + in_page) * d + (p.swizzle ? ((ch ^ (in_page & 7)) * 8) : ch * 8);
             }
         }
-        __syncthreads();
+        cp_async16(sK + row * ROW_BYTES + ch * 16, p.k_pages + src, ok);
+        cp_async16(sV + row * ROW_BYTES + ch * 16, p.v_pages + src, ok);
+        j += rows_per_pass;
+        in_page += rows_per_pass;
+        while (in_page >= ps) { in_page -= ps; ++pi; }
     }
+}
+
+template <int DMAX, bool BULK>
+__global__ void __launch_bounds__(PrefillTiling<DMAX, BULK>::THREADS, PrefillTiling<DMAX, BULK>::BLOCKS_PER_SM)
+attn_prefill_kernel(PrefillParams pp) {
+    pb_grid_dep_launch();
+    using T = PrefillTiling<DMAX, BULK>;
+    const AttnParams& p = pp.a;
+    constexpr int S = T::STAGES;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char* sQ = smem_raw;
+    unsigned char* stages = smem_raw + T::Q_BYTES;
+    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S];
+    __shared__ int s_issued;
+
+    const int G = p.group, d = p.head_dim, ps = p.page_size;
+    const int tpt = PF_ROWS / G;                           // tokens per tile
+    const int tile = blockIdx.x / p.n_kv_heads, kvh = blockIdx.x - tile * p.n_kv_heads;
+    const int r = p.tile_seq[tile], tok0 = p.tile_tok0[tile];
+    const int q_base = p.cu_q[r], q_len = p.cu_q[r + 1] - q_base, pos0 = p.q_start[r];
+    const int n_tok = min(tpt, q_len - tok0);              // tokens of this tile
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int32_t* table = p.block_table + (size_t)p.token_seq[q_base + tok0] * p.table_stride;
+    const int p_min = pos0 + tok0, p_max = pos0 + tok0 + n_tok - 1;
+    const int lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
+    const int kt0 = lo / BN, kt1 = p_max / BN;
+    const int n_tiles = kt1 - kt0 + 1;
+    const int kv_end = p_max + 1;
+
+    if (BULK && threadIdx.x == 0) {
+        s_issued = 0;
+#pragma unroll
+        for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], PF_COMPUTE_THREADS / 32); }
+        mbar_fence_init();
+    }
+    // the batch's index arrays were written before the previous kernel started; q and the newest keys
+    // and values are that kernel's output
+    pb_grid_dep_wait();
+
+    // Q rows: row i -> token tok0 + i / G, head kvh * G + i % G; rows without a token are zero
+    {
+        const int chunks = d >> 3;
+        for (int c = threadIdx.x; c < PF_ROWS * chunks; c += T::THREADS) {
+            const int row = c / chunks, ch = c - row * chunks;
+            const int tl = row / G, hg = row - tl * G;
+            const bool ok = tl < n_tok;
+            const size_t src = ok ? (((size_t)(q_base + tok0 + tl) * p.n_heads + kvh * G + hg) * d + ch * 8) : 0;
+            cp_async16(sQ + row * T::ROW_BYTES + ((BULK ? (ch ^ (row & 7)) : ch) << 4), p.q + src, ok);
+        }
+        cp_async_commit();
+    }
+
+    if (BULK && warp == PF_COMPUTE_THREADS / 32) {
+        cp_async_wait<0>();
+        __syncthreads();                                   // barriers and q are ready
+        // ---------------- loader warp: lane u fetches the u-th run of keys and of values of every tile ----------------
+        const int run_rows = min(ps, BN);                  // tokens one copy brings: a page's run, or 64 of it
+        const int runs = BN / run_rows;
+        const unsigned run_bytes = (unsigned)run_rows * T::ROW_BYTES;
+        auto page_of = [&](int j0, bool& want, size_t& src) {
+            want = lane < runs && j0 <= p_max && j0 + run_rows > lo;       // the run holds a visible key
+            src = 0;
+            if (want) {
+                const int pi = pp.page_shift >= 0 ? (j0 >> pp.page_shift) : (j0 / ps);
+                const int page = table[pi];
+                if (page < 0 || page >= p.num_pages) {
+                    want = false;                          // never read outside the pool; the step is reported as bad
+                    if (p.status) atomicExch(p.status, 6);
+                } else {
+                    src = (((size_t)page * p.n_kv_heads + kvh) * ps + (j0 - pi * ps)) * d;
+                }
+            }
+        };
+        bool want, ok = true;
+        size_t src;
+        page_of(kt0 * BN + lane * run_rows, want, src);
+        int stage = 0, phase = 0;
+#pragma unroll 1
+        for (int i = 0; i < n_tiles; ++i) {
+            ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1);
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            if (lane == 0) *(volatile int*)&s_issued = i + 1;              // the stage's previous tenant has been consumed
+            unsigned char* sK = stages + stage * T::STAGE_BYTES;
+            unsigned char* sV = sK + T::TILE_BYTES;
+            const unsigned n_want = __popc(__ballot_sync(0xffffffffu, want));
+            if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], n_want * run_bytes * 2);
+            __syncwarp();
+            if (want) {
+                bulk_copy_g2s(sK + lane * run_bytes, p.k_pages + src, run_bytes, &full_bar[stage]);
+                bulk_copy_g2s(sV + lane * run_bytes, p.v_pages + src, run_bytes, &full_bar[stage]);
+            }
+            if (i + 1 < n_tiles) page_of((kt0 + i + 1) * BN + lane * run_rows, want, src);   // the next tile's page, ahead of its turn
+            if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 7);
+        return;
+    }
+
+    // ---------------- compute warps ----------------
+    // this thread's two rows, and what the warp's 16 rows can see
+    int row_pos[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int tl = (warp * 16 + g + 8 * h) / G;
+        row_pos[h] = tl < n_tok ? pos0 + tok0 + tl : -1;   // -1: no key is visible
+    }
+    const int tl_first = (warp * 16) / G, tl_last = (warp * 16 + 15) / G;
+    const bool warp_has_rows = tl_first < n_tok;
+    const bool warp_full = tl_last < n_tok;
+    const int wp_min = pos0 + tok0 + tl_first, wp_max = pos0 + tok0 + min(tl_last, n_tok - 1);
+
+    FragOffsets<DMAX, BULK> f;
+    {
+        const int x = lane & 7;
+        const int q_row = warp * 16 + (lane & 15), q_b = lane >> 4;
+        const int k_row = (lane >> 4) * 8 + x, k_b = (lane >> 3) & 1;
+        const int v_row = ((lane >> 3) & 1) * 8 + x, v_b = lane >> 4;
+#pragma unroll
+        for (int j = 0; j < T::NOFF; ++j) {
+            f.q[j] = q_row * T::ROW_BYTES + (BULK ? (((2 * j) ^ (q_b ^ x)) << 4) : q_b * 16);
+            f.k[j] = k_row * T::ROW_BYTES + (BULK ? (((2 * j) ^ (k_b ^ x)) << 4) : k_b * 16);
+            f.v[j] = v_row * T::ROW_BYTES + (BULK ? (((2 * j) ^ (v_b ^ x)) << 4) : v_b * 16);
+        }
+    }
+    const unsigned sQ_a = smem_u32(sQ);
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    auto tile_edge = [&](int key0) {                       // some key of the tile is invisible to some row of the warp
+        return !warp_full || key0 + BN - 1 > wp_min || (p.window > 0 && key0 < wp_max - p.window + 1);
+    };
+    auto tile_unseen = [&](int key0) {                     // no row of the warp sees any key of the tile
+        return !warp_has_rows || key0 > wp_max || (p.window > 0 && key0 + BN - 1 < wp_min - p.window + 1);
+    };
+
+    if constexpr (BULK) {
+        cp_async_wait<0>();
+        __syncthreads();                                   // barriers and q are ready
+        int stage = 0, phase = 0;
+#pragma unroll 1
+        for (int i = 0; i < n_tiles; ++i) {
+            bool landed = true;
+            if (*(volatile int*)&s_issued <= i) {          // not announced yet: the barrier may still be in an older phase
+                const long long t0 = clock64();
+                while (*(volatile int*)&s_issued <= i)
+                    if (clock64() - t0 > (1ll << 31)) { landed = false; break; }
+            }
+            landed = landed && mbar_wait_bounded(&full_bar[stage], phase);
+            if (!__all_sync(0xffffffffu, landed)) {        // gave up waiting: report, do not hang
+                if (lane == 0 && p.status) atomicExch(p.status, 7);
+                break;
+            }
+            unsigned char* sK = stages + stage * T::STAGE_BYTES;
+            unsigned char* sV = sK + T::TILE_BYTES;
+            const int key0 = (kt0 + i) * BN;
+            if (!tile_unseen(key0)) {
+                if (key0 + BN - 1 > p_max || key0 < lo) {
+                    // value rows that no visible key stands for hold whatever the page (or the stage) held: zeros
+                    // instead, so that 0 * (whatever is there) cannot make a NaN.  Every warp writes the same zeros.
+                    for (int rr = lane; rr < BN; rr += 32) {
+                        const int j = key0 + rr;
+                        if (j < lo || j > p_max)
+                            for (int c = 0; c < DMAX / 8; ++c)
+                                *reinterpret_cast<uint4*>(sV + rr * T::ROW_BYTES + c * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async();                   // these ordinary stores come before the bulk copy that refills the stage
+                    __syncwarp();
+                }
+                prefill_tile<DMAX, BULK>(o, m, l, f, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, tile_edge(key0),
+                                         p.window, p.scale_log2, t4);
+            }
+            __syncwarp();
+            if (lane == 0) pf_mbar_arrive(&empty_bar[stage]);              // this warp is done with the stage
+            if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+    } else {
+        const int chunks = d >> 3;
+        const int rows_per_pass = PF_COMPUTE_THREADS / chunks;
+        const int row0 = threadIdx.x / chunks, ch = threadIdx.x - row0 * chunks;
+        load_kv_tile_lsu<DMAX>(stages, stages + T::TILE_BYTES, p, table, kvh, kt0 * BN, lo, kv_end, row0, ch, rows_per_pass);
+        cp_async_commit();
+#pragma unroll 1
+        for (int i = 0; i < n_tiles; ++i) {
+            unsigned char* sK = stages + (i & 1) * T::STAGE_BYTES;
+            unsigned char* sV = sK + T::TILE_BYTES;
+            if (i + 1 < n_tiles) {
+                unsigned char* nK = stages + ((i + 1) & 1) * T::STAGE_BYTES;
+                load_kv_tile_lsu<DMAX>(nK, nK + T::TILE_BYTES, p, table, kvh, (kt0 + i + 1) * BN, lo, kv_end, row0, ch, rows_per_pass);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            const int key0 = (kt0 + i) * BN;
+            if (!tile_unseen(key0))
+                prefill_tile<DMAX, BULK>(o, m, l, f, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, tile_edge(key0),
+                                         p.window, p.scale_log2, t4);
+            __syncthreads();
+        }
+    }
+
     // normalise and store
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -190,29 +486,30 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnParams p)
     }
 }
 
-template <int DMAX> static size_t prefill_smem() { return (size_t)(64 + 4 * BN) * (DMAX + 8) * 2; }
-
-template <int DMAX>
-static int launch_prefill(const AttnParams& p, int n_tiles, cudaStream_t stream) {
+template <int DMAX, bool BULK>
+static int launch_prefill(const PrefillParams& pp, int n_tiles, cudaStream_t stream) {
+    using T = PrefillTiling<DMAX, BULK>;
     static bool configured = false;
-    size_t smem = prefill_smem<DMAX>();
+    const size_t smem = T::SMEM_BYTES;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<DMAX, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return pb_fail("attention_prefill: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    pb_launch(attn_prefill_kernel<DMAX>, dim3(n_tiles, p.n_kv_heads), dim3(ATT_THREADS), smem, stream, p);
+    pb_launch(attn_prefill_kernel<DMAX, BULK>, dim3((unsigned)n_tiles * pp.a.n_kv_heads), dim3(T::THREADS), smem, stream, pp);
     return 0;
 }
 
-
+// Tiles are listed by the host: tile t covers tokens tile_tok0[t] .. of request tile_seq[t]'s portion,
+// 64 / (n_heads / n_kv_heads) tokens each; listing the tiles that see the most keys first shortens the tail.
 PB_API int pb_attention_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                      const int32_t* block_table, int table_stride, const int32_t* positions,
                                      const int32_t* token_seq, const int32_t* cu_q, const int32_t* q_start,
                                      const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size,
                                      int num_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                      float scale, int window, int swizzle, int* status, cudaStream_t stream) {
-    AttnParams p{};
+    PrefillParams pp{};
+    AttnParams& p = pp.a;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.positions = positions; p.token_seq = token_seq;
     p.cu_q = cu_q; p.q_start = q_start; p.tile_seq = tile_seq; p.tile_tok0 = tile_tok0; p.n_splits = 1;
@@ -220,14 +517,24 @@ PB_API int pb_attention_prefill_bf16(const void* q, const void* k_pages, const v
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.swizzle = swizzle;
     if (int e = attn_check_common("attention_prefill", p)) return e;
+    PB_REQUIRE(scale > 0.f, "attention_prefill: scale=%g; the kernel takes the row maximum before scaling", (double)scale);
+    PB_REQUIRE(!swizzle || head_dim % 64 == 0, "attention_prefill: permuted pages need head_dim %% 64 == 0");
     p.group = n_heads / n_kv_heads;
     PB_REQUIRE(p.group <= 64, "attention_prefill: %d query heads per key/value head; at most 64 fit a tile", p.group);
-    PB_REQUIRE(n_tiles >= 0 && n_kv_heads < 65536, "attention_prefill: bad grid");
+    PB_REQUIRE(n_tiles >= 0 && (long long)n_tiles * n_kv_heads < (1ll << 31), "attention_prefill: bad grid");
     if (n_tiles == 0 || n_tokens == 0) return 0;
-    int e = head_dim <= 64 ? launch_prefill<64>(p, n_tiles, stream)
-          : head_dim <= 128 ? launch_prefill<128>(p, n_tiles, stream) : launch_prefill<256>(p, n_tiles, stream);
+    pp.page_shift = -1;
+    for (int s = 0; s < 31; ++s)
+        if ((1 << s) == page_size) pp.page_shift = s;
+    // bulk copies bring whole runs of a page: a run must tile the 64-key tile evenly and start at a multiple
+    // of 8 tokens (the rows then sit at the row numbers their permutation was made for)
+    const bool bulk = swizzle && page_size % 8 == 0 && (BN % page_size == 0 || page_size % BN == 0) &&
+                      (head_dim == 64 || head_dim == 128 || head_dim == 256);
+    int e = bulk ? (head_dim == 64 ? launch_prefill<64, true>(pp, n_tiles, stream)
+                    : head_dim == 128 ? launch_prefill<128, true>(pp, n_tiles, stream) : launch_prefill<256, true>(pp, n_tiles, stream))
+                 : (head_dim <= 64 ? launch_prefill<64, false>(pp, n_tiles, stream)
+                    : head_dim <= 128 ? launch_prefill<128, false>(pp, n_tiles, stream) : launch_prefill<256, false>(pp, n_tiles, stream));
     if (e) return e;
     PB_CHECK_LAUNCH("attention_prefill");
     return 0;
 }
-

@@ -392,7 +392,9 @@ def _check_dispatch(requests, nH, nKV, D, page, window, seed=0, trimmed_below=No
 
 
 @pytest.mark.parametrize("nH,nKV,D,page", [(4, 2, 16, 4), (6, 2, 32, 8), (5, 1, 48, 16), (8, 8, 64, 16), (3, 3, 80, 16),
-                                           (32, 8, 128, 16), (2, 1, 256, 32), (16, 2, 128, 16), (7, 7, 112, 16)])
+                                           (32, 8, 128, 16), (2, 1, 256, 32), (16, 2, 128, 16), (7, 7, 112, 16),
+                                           (4, 2, 64, 24), (8, 2, 128, 48), (4, 1, 128, 64), (6, 3, 64, 128),
+                                           (4, 4, 192, 16), (4, 1, 128, 8), (2, 2, 256, 40)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_attention_prefill_tensor_cores(nH, nKV, D, page, window):
     # whole prompts, a portion that continues a cached prefix, single tokens in between, a two-token portion
@@ -401,7 +403,9 @@ def test_attention_prefill_tensor_cores(nH, nKV, D, page, window):
 
 
 @pytest.mark.parametrize("nH,nKV,D,page", [(4, 2, 16, 4), (6, 2, 32, 8), (5, 1, 48, 16), (8, 8, 64, 16), (3, 3, 80, 16),
-                                           (32, 8, 128, 16), (2, 1, 256, 32), (16, 1, 128, 16), (7, 7, 112, 16)])
+                                           (32, 8, 128, 16), (2, 1, 256, 32), (16, 1, 128, 16), (7, 7, 112, 16),
+                                           (4, 2, 64, 24), (8, 2, 128, 48), (4, 1, 128, 64), (6, 3, 64, 128),
+                                           (4, 4, 192, 16), (4, 1, 128, 8), (2, 2, 256, 40)])
 @pytest.mark.parametrize("window", [None, 70])
 @pytest.mark.parametrize("splits", [None, 1, 3, 8])
 def test_attention_decode_tensor_cores(monkeypatch, nH, nKV, D, page, window, splits):
