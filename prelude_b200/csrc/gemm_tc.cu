@@ -4,13 +4,15 @@
 //   A: [rows_a, K] bfloat16, K contiguous     B: [rows_b, K] bfloat16, K contiguous
 //   C[i, j] = sum_k A[i, k] * B[j, k]          float32 accumulation
 //
-// One kernel serves both shapes of a linear layer y = x W^T:
-//   * many tokens (prompt portions):  A = x (128 tokens per tile), B = W (256
-//     features per tile), y[i, j] = C[i, j];
-//   * few tokens (decode steps):      A = W (128 features per tile), B = x (the
-//     batch padded to 16, 32 or 64), y[j, i] = C[i, j] - the weight matrix is the
-//     128-row operand, so every weight byte is read once and the tensor cores'
-//     row dimension is full whatever the batch size.
+// A linear layer y = x W^T is A = x (128 tokens per tile), B = W (up to 256
+// features per tile), for prompt portions and for decode steps alike.  A decode
+// step has a handful of tokens: TMA fills the rows of the A tile that do not
+// exist with zeros, and the step is a stream over W.  The other orientation
+// (W as the 128-row operand, the batch as a 16-column B) was measured and
+// dropped: an MMA of 128 rows takes about 128 cycles however few columns it
+// has, so with 16 columns the tensor pipe consumes W at 28 bytes a cycle, no
+// faster than memory delivers it, while with 256 features per instruction it
+// consumes 64 bytes a cycle.
 // (The reference sends these products to DeepGEMM / CUTLASS / cuBLAS,
 // crates/prelude-cuda/src/ops/gemm.rs:35-137; its sm_100 path is
 // crates/prelude-cuda/deepgemm/src/sm100_bf16.cuh:10-205.)
@@ -124,17 +126,54 @@ __device__ __forceinline__ uint32_t tc_instr_desc(int bn) {
 }
 
 struct TcParams {
-    void* out;                  // bfloat16 or float32
-    const float* bias;          // per feature, or null
+    void* out;                  // [rows_a, rows_b] bfloat16 or float32
+    const float* bias;          // per column of out, or null
     float* scratch;             // [grid][2][128][BN] partial tiles
     int* counters;              // [tiles], zero on entry and on exit
     int* status;
     long long ldo;
     int rows_a, rows_b, K;
     int tiles_a, tiles_b, kblocks, items_per_block;
-    int transposed;             // 1: out[j, i] = C[i, j] (A holds the weights); 0: out[i, j] = C[i, j]
+    int b_is_constant;          // B is written by no kernel (weights): its loads need not wait for the previous kernel
     int out_f32;
 };
+
+// N consecutive columns of one output row, from float32 sums
+template <int N>
+__device__ __forceinline__ void tc_store_n(const TcParams& p, int gi, int gj0, const float* v) {
+    if (p.out_f32) {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)gi * p.ldo + gj0;
+        if (gj0 + N <= p.rows_b && !p.bias && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < N; ++j)
+                if (gj0 + j < p.rows_b) o[j] = v[j] + (p.bias ? p.bias[gj0 + j] : 0.f);
+        }
+    } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)gi * p.ldo + gj0;
+        if (gj0 + N <= p.rows_b && !p.bias && ((reinterpret_cast<uintptr_t>(o) & (2 * N - 1)) == 0)) {
+            unsigned w[N / 2];
+#pragma unroll
+            for (int j = 0; j < N / 2; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<unsigned*>(&h);
+            }
+            if constexpr (N == 4) {
+                *reinterpret_cast<uint2*>(o) = make_uint2(w[0], w[1]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < N / 2; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < N; ++j)
+                if (gj0 + j < p.rows_b) o[j] = __float2bfloat16_rn(v[j] + (p.bias ? p.bias[gj0 + j] : 0.f));
+        }
+    }
+}
+__device__ __forceinline__ void tc_store16(const TcParams& p, int gi, int gj0, const float* v) { tc_store_n<16>(p, gi, gj0, v); }
 
 template <int BN>
 struct TcShared {
@@ -174,15 +213,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_holder;
-    // barriers, tensor memory and descriptors are set up; from here on the operands are read
-    pb_grid_dep_wait();
-
+    // Barriers, tensor memory and descriptors are set up.  Every thread waits for the kernel before this one
+    // before it first touches memory that a kernel writes; weights are written by no kernel, so when B holds
+    // them the producer starts their stream before that wait and fills the whole ring while the previous
+    // kernel is still finishing.
     if (warp == 4) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             int fill = 0;
             bool ok = true;
-            for (int it = my_begin; it < my_end && ok; ++it, ++fill) {
+            const int ahead = p.b_is_constant ? min(S::STAGES, my_end - my_begin) : 0;
+            for (int j = 0; j < ahead; ++j) {
+                const int it = my_begin + j;
+                const int tile = it / p.kblocks, kb = it - tile * p.kblocks;
+                tc_mbar_expect_tx(&full_bar[j], S::STAGE_BYTES);
+                tc_tma_load_2d(smem + j * S::STAGE_BYTES + TC_A_BYTES, &map_b, kb * TC_BK, (tile / p.tiles_a) * BN, &full_bar[j]);
+            }
+            pb_grid_dep_wait();
+            for (int j = 0; j < ahead; ++j) {
+                const int it = my_begin + j;
+                const int tile = it / p.kblocks, kb = it - tile * p.kblocks;
+                tc_tma_load_2d(smem + j * S::STAGE_BYTES, &map_a, kb * TC_BK, (tile % p.tiles_a) * TC_BM, &full_bar[j]);
+            }
+            fill = ahead;
+            for (int it = my_begin + ahead; it < my_end && ok; ++it, ++fill) {
                 const int tile = it / p.kblocks, kb = it - tile * p.kblocks;
                 const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;      // A tiles vary fastest: neighbours share the B panel
                 const int stage = fill % S::STAGES;
@@ -196,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!ok && p.status) atomicExch(p.status, 8);
         }
     } else if (warp == 5) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer: reads shared and tensor memory only ----------------
         if (lane == 0) {
             const uint32_t idesc = tc_instr_desc(BN);
             int fill = 0, seg = 0;
@@ -229,6 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ---------------- epilogue: 4 warps, 128 accumulator rows ----------------
+        pb_grid_dep_wait();                                                      // the output and the scratch may still be in use
         const int row = warp * 32 + lane;                                        // row of the tile = tensor-memory lane
         int seg = 0;
         bool ok = true;
@@ -245,54 +300,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const bool whole = (it == tile_begin) && (seg_end == tile_end);
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(warp * 32) << 16);
+            const int rows_here = min(TC_BM, p.rows_a - ta * TC_BM);             // rows of the tile that exist
             const int gi = ta * TC_BM + row;                                     // row of A
-            float* part = p.scratch + ((size_t)blockIdx.x * 2 + (it == my_begin ? 0 : 1)) * TC_BM * BN + (size_t)row * BN;
+            float* part = p.scratch + ((size_t)blockIdx.x * 2 + (it == my_begin ? 0 : 1)) * TC_BM * BN;
+            // a decode step has a handful of rows: warps whose 32 rows are all padding skip the loads
+            if (warp * 32 < rows_here) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                tc_tmem_ld16(taddr + c0, v);
-                if (!whole) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tc_tmem_ld16(taddr + c0, v);
+                    if (gi < p.rows_a) {
+                        if (!whole) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        *reinterpret_cast<float4*>(part + c0 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                } else if (gi >= p.rows_a) {
-                    // a row beyond the matrix: nothing to store
-                } else if (p.transposed) {
-                    const float b = p.bias ? p.bias[gi] : 0.f;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int gj = tb * BN + c0 + j;
-                        if (gj < p.rows_b) {
-                            if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)gj * p.ldo + gi] = v[j] + b;
-                            else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)gj * p.ldo + gi] = __float2bfloat16_rn(v[j] + b);
-                        }
-                    }
-                } else {
-                    const int gj0 = tb * BN + c0;
-                    if (p.out_f32) {
-                        float* o = reinterpret_cast<float*>(p.out) + (size_t)gi * p.ldo + gj0;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (gj0 + j < p.rows_b) o[j] = v[j] + (p.bias ? p.bias[gj0 + j] : 0.f);
-                    } else {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)gi * p.ldo + gj0;
-                        if (gj0 + 16 <= p.rows_b && !p.bias && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-                            uint4 w0, w1;
-                            __nv_bfloat162 h[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            w0 = make_uint4(*(unsigned*)&h[0], *(unsigned*)&h[1], *(unsigned*)&h[2], *(unsigned*)&h[3]);
-                            w1 = make_uint4(*(unsigned*)&h[4], *(unsigned*)&h[5], *(unsigned*)&h[6], *(unsigned*)&h[7]);
-                            reinterpret_cast<uint4*>(o)[0] = w0;
-                            reinterpret_cast<uint4*>(o)[1] = w1;
+                            for (int q = 0; q < 4; ++q)
+                                *reinterpret_cast<float4*>(part + (size_t)row * BN + c0 + 4 * q) =
+                                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                         } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (gj0 + j < p.rows_b) o[j] = __float2bfloat16_rn(v[j] + (p.bias ? p.bias[gj0 + j] : 0.f));
+                            tc_store16(p, gi, tb * BN + c0, v);
                         }
                     }
+                    __syncwarp();                                                // the next tensor-memory load needs the whole warp
                 }
-                __syncwarp();                                                    // the next tensor-memory load needs the whole warp
             }
             // the accumulator may be overwritten
             tc_fence_before();
@@ -311,25 +339,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_bar_epilogue();
                 if (s_flag) {
                     __threadfence();
-                    for (int c0 = 0; c0 < BN; c0 += 4) {
+                    // all 128 threads share the rows that exist: four columns each, the partial tiles of
+                    // the blocks c_first..c_last added in that order (independent loads, four in flight)
+                    const int quads = BN / 4;
+                    for (int idx = threadIdx.x; idx < rows_here * quads; idx += 128) {
+                        const int r = idx / quads, c4 = (idx - r * quads) * 4;
                         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int c = c_first; c <= c_last; ++c) {
-                            const int slot = (max(c * p.items_per_block, tile_begin) == c * p.items_per_block) ? 0 : 1;
-                            const float4 x = __ldcg(reinterpret_cast<const float4*>(
-                                p.scratch + ((size_t)c * 2 + slot) * TC_BM * BN + (size_t)row * BN + c0));
-                            sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
-                        }
-                        if (gi >= p.rows_a) continue;
-                        const float vv[4] = {sum.x, sum.y, sum.z, sum.w};
+                        for (int c = c_first; c <= c_last; c += 4) {
+                            float4 x[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int gj = tb * BN + c0 + j;
-                            if (gj >= p.rows_b) continue;
-                            const float b = p.bias ? p.bias[p.transposed ? gi : gj] : 0.f;
-                            const size_t at = p.transposed ? ((size_t)gj * p.ldo + gi) : ((size_t)gi * p.ldo + gj);
-                            if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = vv[j] + b;
-                            else reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(vv[j] + b);
+                            for (int u = 0; u < 4; ++u) {
+                                const int cc = min(c + u, c_last);
+                                const int slot = (cc * p.items_per_block >= tile_begin) ? 0 : 1;
+                                x[u] = __ldcg(reinterpret_cast<const float4*>(
+                                    p.scratch + ((size_t)cc * 2 + slot) * TC_BM * BN + (size_t)r * BN + c4));
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                if (c + u <= c_last) { sum.x += x[u].x; sum.y += x[u].y; sum.z += x[u].z; sum.w += x[u].w; }
                         }
+                        const float vv[4] = {sum.x, sum.y, sum.z, sum.w};
+                        tc_store_n<4>(p, ta * TC_BM + r, tb * BN + c4, vv);
                     }
                 }
                 tc_bar_epilogue();
@@ -435,12 +465,14 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     return 0;
 }
 
-// C = A B^T.  transposed = 0: out[i * ldo + j] = C[i, j];  transposed = 1: out[j * ldo + i] = C[i, j].
-// bias: per feature (per column of out), float32 or null.  out_f32: 1 for float32 output, 0 for bfloat16.
+// out[i * ldo + j] = sum_k A[i, k] B[j, k] (+ bias[j]).
+// bias: per column of out, float32 or null.  out_f32: 1 for float32 output, 0 for bfloat16.
+// b_is_constant: 1 when no kernel writes B (a weight matrix): its stream then starts before the
+// previous kernel on the stream has finished.
 // scratch: pb_gemm_tc_scratch_bytes(...) bytes whose first 4 * TC_MAX_TILES bytes (the counters) are zero
 // before the first call; every call leaves them zero, so calls on one stream may share the buffer.
 PB_API int pb_gemm_tc_bf16(const void* A, const void* B, const float* bias, void* out, int rows_a, int rows_b, int K,
-                           long long lda, long long ldb, long long ldo, int transposed, int out_f32, void* scratch,
+                           long long lda, long long ldb, long long ldo, int b_is_constant, int out_f32, void* scratch,
                            int* status, cudaStream_t stream) {
     PB_REQUIRE(pb_gemm_tc_supported(rows_a, rows_b, K, lda, ldb),
                "gemm_tc: rows_a=%d rows_b=%d K=%d lda=%lld ldb=%lld not taken (rows must be 16-byte aligned)", rows_a, rows_b, K, lda, ldb);
@@ -450,7 +482,7 @@ PB_API int pb_gemm_tc_bf16(const void* A, const void* B, const float* bias, void
     int bn, blocks;
     tc_plan(rows_a, rows_b, K, &bn, &p.tiles_a, &p.tiles_b, &p.kblocks, &p.items_per_block, &blocks);
     p.out = out; p.bias = bias; p.status = status; p.ldo = ldo; p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
-    p.transposed = transposed; p.out_f32 = out_f32;
+    p.b_is_constant = b_is_constant; p.out_f32 = out_f32;
     p.counters = (int*)scratch;
     p.scratch = (float*)((char*)scratch + (size_t)TC_MAX_TILES * 4);
     CUtensorMap ma, mb;

@@ -463,41 +463,59 @@ def test_tensor_core_attention_refuses_or_falls_back():
 # the weight-streaming product for decode steps
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("N,K_", [(2560, 4096), (19456, 2560), (6144, 2560), (2560, 9728), (48, 64), (16, 32),
-                                  (176, 96), (1008, 1504)])
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
-def test_gemm_skinny(M, N, K_):
-    from prelude_b200.ops.linear import gemm_skinny
+                                  (176, 96), (1008, 1504), (7, 32), (151936, 2560), (333, 2064), (333, 2080)])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+def test_gemm_stream(M, N, K_):
+    from prelude_b200.ops.linear import gemm_stream, stream_takes, tc_status
     x, w, b = rnd(M, K_, dtype=torch.bfloat16, seed=21), rnd(N, K_, dtype=torch.bfloat16, seed=22, scale=0.05), rnd(N, seed=23)
+    if not stream_takes(x, w):              # K no multiple of 32, or x too long to fit beside the ring
+        assert K_ % 32 or (M > 8 and K_ > 6000)
+        return
     want = x.double() @ w.double().T
     scale = float(want.abs().max())
-    got = gemm_skinny(x, w)
+    got = gemm_stream(x, w)
     assert (got.double() - want).abs().max() <= tol(torch.bfloat16, scale)
-    assert torch.equal(gemm_skinny(x, w), got)                       # counters are back at zero, same sums
-    got_b = gemm_skinny(x, w, b)
-    assert (got_b.double() - (want + b.double())).abs().max() <= tol(torch.bfloat16, float((want + b.double()).abs().max()))
-    if M > 1:                                                        # a row does not depend on the rest of the batch
-        assert torch.equal(gemm_skinny(x[M - 1:M].contiguous(), w), got[M - 1:M])
+    assert torch.equal(gemm_stream(x, w), got)
+    got32 = gemm_stream(x, w, b, torch.float32)
+    assert got32.dtype == torch.float32
+    assert (got32.double() - (want + b.double())).abs().max() <= 2e-3 * max(1.0, scale)
+    if M > 1:            # a row does not depend on the rest of the batch, beyond rounding (K is cut differently)
+        alone = gemm_stream(x[M - 1:M].contiguous(), w)
+        assert (alone.double() - got[M - 1:M].double()).abs().max() <= tol(torch.bfloat16, scale)
     wide = rnd(M, K_ + 64, dtype=torch.bfloat16, seed=24)            # x as a view into a wider tensor
-    assert torch.equal(gemm_skinny(wide[:, 32:32 + K_], w), gemm_skinny(wide[:, 32:32 + K_].contiguous(), w))
+    assert torch.equal(gemm_stream(wide[:, 32:32 + K_], w), gemm_stream(wide[:, 32:32 + K_].contiguous(), w))
+    assert int(tc_status(x.device).item()) == 0
 
 
-def test_gemm_skinny_refuses_other_shapes_and_linear_falls_back(monkeypatch):
-    from prelude_b200.ops import linear as linear_module
+def test_gemm_stream_finds_the_one_weight_that_matters():
+    # one large product at the far end of K and of N, everything else small: a lost chunk or row shows
+    from prelude_b200.ops.linear import gemm_stream
+    M, N, K_ = 5, 2563 - 3, 4096
+    x, w = rnd(M, K_, dtype=torch.bfloat16, seed=1, scale=0.01), rnd(N, K_, dtype=torch.bfloat16, seed=2, scale=0.01)
+    for (m, n, k) in [(0, 0, 0), (4, N - 1, K_ - 1), (2, 1297, 2047), (3, 17, 2048), (1, N - 17, 2815), (0, 8, 31), (4, 7, 32)]:
+        x2, w2 = x.clone(), w.clone()
+        x2[m, k], w2[n, k] = 8.0, 8.0
+        got = gemm_stream(x2, w2)
+        assert abs(float(got[m, n]) - 64.0) < 1.0
+        got[m, n] = 0
+        assert float(got.abs().max()) < 1.0
+
+
+def test_gemm_stream_refuses_other_shapes_and_linear_falls_back():
     from prelude_b200.ops.library import KernelLibraryError
-    from prelude_b200.ops.linear import gemm_skinny, linear, skinny_takes
-    monkeypatch.setattr(linear_module, "SKINNY_MAX_ROWS", 16)
-    x, w = rnd(4, 72, dtype=torch.bfloat16), rnd(40, 72, dtype=torch.bfloat16)
-    assert not skinny_takes(x, w)
+    from prelude_b200.ops.linear import gemm_stream, linear, stream_takes
+    x, w = rnd(4, 72, dtype=torch.bfloat16), rnd(40, 72, dtype=torch.bfloat16)      # K is no multiple of 16
+    assert not stream_takes(x, w)
     with pytest.raises(KernelLibraryError, match="not taken"):
-        gemm_skinny(x, w)
+        gemm_stream(x, w)
     want = x.double() @ w.double().T
     assert (linear(x, w).double() - want).abs().max() <= tol(torch.bfloat16, float(want.abs().max()))
-    assert not skinny_takes(rnd(100, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
-    assert skinny_takes(rnd(8, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
+    assert not stream_takes(rnd(17, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
+    assert stream_takes(rnd(8, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
 
 
 # ---------------------------------------------------------------------------------------
-# the tcgen05 product (TMA, tensor memory), in both orientations
+# the tcgen05 product (TMA, tensor memory)
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K_", [(8, 128, 64), (1, 2560, 4096), (8, 6144, 2560), (5, 200, 72), (33, 2560, 9728),
                                     (64, 1000, 1024), (16, 331, 200), (65, 256, 64), (128, 256, 256), (300, 2560, 4096),
