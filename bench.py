@@ -213,7 +213,9 @@ def time_e2e(engine, cfg, batch, steps):
     import torch
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, cfg["vocab_size"], (PREFIX_LEN,), generator=g).tolist() for _ in range(batch)]
-    # warm up outside the timed call: the decode step is captured per batch size at its first use
+    # warm up outside the timed call: the decode step is captured per batch size at its first use, and
+    # requests that finish a step apart leave smaller batches behind
+    engine.warmup(range(1, batch + 1))
     engine.generate([p[:32] for p in prompts], temperature=0.0, max_new_tokens=4, ignore_eos=True)
     t0 = time.time()
     res = engine.generate(prompts, temperature=0.0, max_new_tokens=steps + 1, ignore_eos=True)

@@ -130,6 +130,27 @@ class Engine:
     def stats(self) -> EngineStats:
         return self._stats
 
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Capture the decode step for the given batch sizes (default: every size up to
+        ``max_running_requests`` and ``cuda_graph_max_bs``) before the first request needs
+        them: a capture takes a few hundred milliseconds, which a request would otherwise
+        wait for the first time its batch size comes up.  Runs short dummy generations;
+        returns the sizes captured.  (The reference warms its graphs up at start-up as well,
+        crates/prelude-cuda/src/cuda_graph.rs:84-112, one capture per batch size up to cuda_graph_max_bs.)"""
+        if self.graphs is None:
+            return []
+        limit = min(self.graphs.max_bs, self.sched_config.max_running_requests)
+        sizes = sorted({int(b) for b in (batch_sizes if batch_sizes is not None else range(1, limit + 1))
+                        if 1 <= int(b) <= limit})
+        done = []
+        for bs in sizes:
+            if bs in self.graphs.graphs and self.graphs.graphs[bs].graph is not None:
+                continue
+            self.generate([[0]] * bs, temperature=0.0, max_new_tokens=3, ignore_eos=True)
+            if bs in self.graphs.graphs:
+                done.append(bs)
+        return done
+
     # -- generation ---------------------------------------------------------------------
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                  sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None, *,
