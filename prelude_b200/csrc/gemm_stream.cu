@@ -24,6 +24,12 @@
 //    instruction), both fetched from rows padded by 16 bytes; every warp keeps
 //    four independent chains of sums.  When a 16-feature tile has seen all of K
 //    the warps' sums are added through shared memory and stored.
+//  * Where K is long and the output narrow (the down projection), x would crowd
+//    the ring out of shared memory and every block would fetch all of it.  K can
+//    then be cut into a few parts: the grid gets a second dimension, every part
+//    works on its columns of W and x only and writes float32 partial sums of
+//    its own, and whoever reads the output adds the parts (the residual add
+//    does).  Nothing waits for anything.
 //  * Waits on barriers are bounded in time; a warp that gives up raises the
 //    status word and the block goes on to its end.
 // The tensor-memory kernel (gemm_tc.cu) is the wrong tool here: its instruction
@@ -56,6 +62,7 @@ struct GsParams {
     int n_chunks;           // chunks of K per row
     int stages;
     int out_f32;
+    long long split_stride; // elements between the partial outputs of the splits of K (gridDim.y of them)
     int* status;
 };
 
@@ -76,6 +83,15 @@ __device__ __forceinline__ void ldmatrix_x2(unsigned& r0, unsigned& r1, unsigned
 template <int MT>
 __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) {
     pb_grid_dep_launch();
+    if (gridDim.y > 1) {
+        // K is cut into gridDim.y equal parts (p.K is the length of one); part s multiplies its columns of W with
+        // its columns of x and writes a partial output of its own, which the reader adds up
+        const int s = blockIdx.y;
+        p.W += (size_t)s * p.K;
+        p.X += (size_t)s * p.K;
+        p.out = reinterpret_cast<float*>(p.out) + (size_t)s * p.split_stride;
+        if (s > 0) p.bias = nullptr;
+    }
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t full_bar[GS_MAX_STAGES], empty_bar[GS_MAX_STAGES], x_bar;
     __shared__ int s_issued, s_dead;
@@ -299,17 +315,25 @@ PB_API int pb_gemm_stream_supported(int M, int N, int K, long long ldw, long lon
     return gs_plan(M, K, &ks, &nc, &st, &smem) ? 1 : 0;
 }
 
+// splits > 1 cuts K into that many equal parts (K %% (16 * splits) == 0): out is then float32
+// [splits][M][ldo-strided N] with split_stride elements between the parts, and the caller adds them.
 PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, void* out, int M, int N, int K,
-                               long long ldx, long long ldw, long long ldo, int out_f32, int* status, cudaStream_t stream) {
-    PB_REQUIRE(pb_gemm_stream_supported(M, N, K, ldw, ldx),
-               "gemm_stream: M=%d N=%d K=%d not taken (M <= 16, K %% 16 == 0, 16-byte aligned rows, x must fit in shared memory)", M, N, K);
+                               long long ldx, long long ldw, long long ldo, int out_f32, int splits, long long split_stride,
+                               int* status, cudaStream_t stream) {
+    PB_REQUIRE(splits >= 1 && splits <= 16 && (splits == 1 || K % (16 * splits) == 0), "gemm_stream: K=%d cannot be cut into %d parts of whole 16-element steps", K, splits);
+    PB_REQUIRE(splits == 1 || (out_f32 && split_stride >= (long long)(M - 1) * ldo + N), "gemm_stream: partial sums are float32, %d apart at least", M * N);
+    const int k_part = K / splits;
+    PB_REQUIRE(pb_gemm_stream_supported(M, N, k_part, ldw, ldx),
+               "gemm_stream: M=%d N=%d K=%d not taken (M <= 16, K %% 16 == 0, 16-byte aligned rows, x must fit in shared memory)", M, N, k_part);
     PB_REQUIRE(X && W && out && pb_aligned(X, 16) && pb_aligned(W, 16), "gemm_stream: null or unaligned pointer");
     GsParams p{};
     p.W = (const __nv_bfloat16*)W; p.X = (const __nv_bfloat16*)X; p.out = out; p.bias = bias;
-    p.ldw = ldw; p.ldx = ldx; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.status = status;
+    p.ldw = ldw; p.ldx = ldx; p.ldo = ldo; p.M = M; p.N = N; p.K = k_part; p.out_f32 = out_f32; p.status = status;
+    p.split_stride = split_stride;
     size_t smem;
-    gs_plan(M, K, &p.ks, &p.n_chunks, &p.stages, &smem);
-    int blocks = gs_sms();
+    gs_plan(M, k_part, &p.ks, &p.n_chunks, &p.stages, &smem);
+    int blocks = gs_sms() / splits;
+    if (blocks < 1) blocks = 1;
     if (blocks > (N + 7) / 8) blocks = (N + 7) / 8;           // at least 8 features per block
     static bool configured = false;
     if (!configured) {
@@ -318,8 +342,8 @@ PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, 
         if (e != cudaSuccess) return pb_fail("gemm_stream: cannot get %d bytes of shared memory: %s", GS_SMEM_LIMIT, cudaGetErrorString(e));
         configured = true;
     }
-    if (M <= 8) pb_launch(gemm_stream_kernel<1>, dim3(blocks), dim3(GS_THREADS), smem, stream, p);
-    else pb_launch(gemm_stream_kernel<2>, dim3(blocks), dim3(GS_THREADS), smem, stream, p);
+    if (M <= 8) pb_launch(gemm_stream_kernel<1>, dim3(blocks, splits), dim3(GS_THREADS), smem, stream, p);
+    else pb_launch(gemm_stream_kernel<2>, dim3(blocks, splits), dim3(GS_THREADS), smem, stream, p);
     PB_CHECK_LAUNCH("gemm_stream");
     return 0;
 }

@@ -26,8 +26,8 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 }
 
 template <typename TX, typename TY>
-__global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__ res, const float* __restrict__ w,
-                                   TY* __restrict__ y, int width, float eps) {
+__global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride, float* __restrict__ res,
+                                   const float* __restrict__ w, TY* __restrict__ y, int width, float eps) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float red[32];
@@ -38,7 +38,8 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
     if (x != nullptr) {
         const TX* xr = x + row * width;
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
-            float v = r[i] + pb_ld(xr + i);
+            float v = r[i];
+            for (int s = 0; s < n_parts; ++s) v += pb_ld(xr + s * part_stride + i);     // the parts in ascending order
             r[i] = v;
             ss += v * v;
         }
@@ -56,8 +57,8 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
 // Four elements per thread and access, the row kept in registers between the
 // two passes.  width % 4 == 0, width <= 4 * blockDim * ITERS.
 template <typename TX, typename TY, int ITERS>
-__global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, float* __restrict__ res, const float* __restrict__ w,
-                                        TY* __restrict__ y, int width, float eps) {
+__global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride, float* __restrict__ res,
+                                        const float* __restrict__ w, TY* __restrict__ y, int width, float eps) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float red[32];
@@ -79,8 +80,10 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, float* __restr
                     float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
                     v.x += a.x; v.y += a.y; v.z += b.x; v.w += b.y;
                 } else {
-                    float4 a = *reinterpret_cast<const float4*>(xr);
-                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    for (int s = 0; s < n_parts; ++s) {                              // the parts in ascending order
+                        float4 a = *reinterpret_cast<const float4*>(xr + s * part_stride);
+                        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    }
                 }
                 r4[i] = v;
             }
@@ -119,33 +122,42 @@ static int norm_threads(int width) {
 }
 
 template <typename TX, typename TY>
-static int launch_add_rmsnorm(const void* x, float* res, const float* w, void* y, int rows, int width, float eps,
-                              cudaStream_t stream) {
+static int launch_add_rmsnorm(const void* x, int n_parts, size_t part_stride, float* res, const float* w, void* y, int rows,
+                              int width, float eps, cudaStream_t stream) {
     int threads = norm_threads(width);
     bool vec = width % 4 == 0 && pb_aligned(res, 16) && pb_aligned(w, 16) && pb_aligned(y, 8 * sizeof(TY) / 2) &&
-               (x == nullptr || pb_aligned(x, 8 * sizeof(TX) / 2)) && width <= 4 * threads * 8;
+               (x == nullptr || (pb_aligned(x, 8 * sizeof(TX) / 2) && part_stride % 4 == 0)) && width <= 4 * threads * 8;
     if (vec) {
         int iters = (width / 4 + threads - 1) / threads;
         if (iters <= 2)
-            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 2>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 2>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
         else if (iters <= 4)
-            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 4>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 4>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
         else
-            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 8>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 8>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
     } else {
-        pb_launch(add_rmsnorm_kernel<TX, TY>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, res, w, (TY*)y, width, eps);
+        pb_launch(add_rmsnorm_kernel<TX, TY>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
     }
     return 0;
 }
 
 // res[rows, width] float32 (updated in place when x is given); x may be null
-// (no add); w float32 [width]; y [rows, width] of type dtype.  x has type dtype.
-PB_API int pb_add_rmsnorm(const void* x, float* res, const float* w, void* y, int dtype, int rows, int width,
-                          float eps, cudaStream_t stream) {
+// (no add); w float32 [width]; y [rows, width] of type dtype.  x has type dtype,
+// or, with x_parts > 0, it is x_parts float32 arrays [rows, width], part_stride
+// elements apart, whose sum is what is added (the partial sums of a product
+// whose K was cut into parts).
+PB_API int pb_add_rmsnorm(const void* x, int x_parts, long long part_stride, float* res, const float* w, void* y, int dtype,
+                          int rows, int width, float eps, cudaStream_t stream) {
     PB_REQUIRE(rows >= 0 && width > 0, "add_rmsnorm: bad sizes rows=%d width=%d", rows, width);
     PB_REQUIRE(res && w && y, "add_rmsnorm: null pointer");
+    PB_REQUIRE(x_parts >= 0 && x_parts <= 64 && (x_parts == 0 || (x && part_stride >= (long long)rows * width)),
+               "add_rmsnorm: %d parts %lld apart", x_parts, part_stride);
     if (rows == 0) return 0;
-    PB_DISPATCH_DTYPE(dtype, T, (launch_add_rmsnorm<T, T>(x, res, w, y, rows, width, eps, stream)));
+    if (x_parts > 0) {
+        PB_DISPATCH_DTYPE(dtype, T, (launch_add_rmsnorm<float, T>(x, x_parts, (size_t)part_stride, res, w, y, rows, width, eps, stream)));
+    } else {
+        PB_DISPATCH_DTYPE(dtype, T, (launch_add_rmsnorm<T, T>(x, 1, 0, res, w, y, rows, width, eps, stream)));
+    }
     PB_CHECK_LAUNCH("add_rmsnorm");
     return 0;
 }
@@ -156,9 +168,10 @@ PB_API int pb_add_rmsnorm(const void* x, float* res, const float* w, void* y, in
 // final norm, crates/prelude-core/src/models/commons/mod.rs:227-243; the order
 // does not change the values).
 template <typename TX, typename TY>
-__global__ void gather_add_rmsnorm_kernel(const TX* __restrict__ x, const float* __restrict__ res,
-                                          const int32_t* __restrict__ rows, const float* __restrict__ w,
-                                          TY* __restrict__ y, int width, int n_rows_total, float eps) {
+__global__ void gather_add_rmsnorm_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride,
+                                          const float* __restrict__ res, const int32_t* __restrict__ rows,
+                                          const float* __restrict__ w, TY* __restrict__ y, int width, int n_rows_total,
+                                          float eps) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float red[32];
@@ -170,27 +183,39 @@ __global__ void gather_add_rmsnorm_kernel(const TX* __restrict__ x, const float*
     }
     const float* r = res + (size_t)src * width;
     const TX* xr = x ? x + (size_t)src * width : nullptr;
+    auto value = [&](int i) {
+        float v = r[i];
+        if (xr) for (int s = 0; s < n_parts; ++s) v += pb_ld(xr + s * part_stride + i);   // the parts in ascending order
+        return v;
+    };
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = r[i] + (xr ? pb_ld(xr + i) : 0.f);
+        float v = value(i);
         ss += v * v;
     }
     float total = block_sum(ss, red);
     float inv = 1.0f / sqrtf(total / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = r[i] + (xr ? pb_ld(xr + i) : 0.f);
-        pb_st(out + i, v * inv * w[i]);
-    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, value(i) * inv * w[i]);
 }
 
-PB_API int pb_gather_add_rmsnorm(const void* x, const float* res, const int32_t* rows, const float* w, void* y,
-                                 int dtype, int n_out, int n_rows_total, int width, float eps, cudaStream_t stream) {
+// x as for pb_add_rmsnorm: of type dtype, or x_parts float32 arrays to be added up.
+PB_API int pb_gather_add_rmsnorm(const void* x, int x_parts, long long part_stride, const float* res, const int32_t* rows,
+                                 const float* w, void* y, int dtype, int n_out, int n_rows_total, int width, float eps,
+                                 cudaStream_t stream) {
     PB_REQUIRE(n_out >= 0 && width > 0 && n_rows_total >= 0, "gather_add_rmsnorm: bad sizes");
     PB_REQUIRE(res && rows && w && y, "gather_add_rmsnorm: null pointer");
+    PB_REQUIRE(x_parts >= 0 && x_parts <= 64 && (x_parts == 0 || (x && part_stride >= (long long)n_rows_total * width)),
+               "gather_add_rmsnorm: %d parts %lld apart", x_parts, part_stride);
     if (n_out == 0) return 0;
-    PB_DISPATCH_DTYPE(dtype, T,
-        (pb_launch(gather_add_rmsnorm_kernel<T, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream, 
-            (const T*)x, res, rows, w, (T*)y, width, n_rows_total, eps)));
+    if (x_parts > 0) {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(gather_add_rmsnorm_kernel<float, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream,
+                (const float*)x, x_parts, (size_t)part_stride, res, rows, w, (T*)y, width, n_rows_total, eps)));
+    } else {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(gather_add_rmsnorm_kernel<T, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream,
+                (const T*)x, 1, (size_t)0, res, rows, w, (T*)y, width, n_rows_total, eps)));
+    }
     PB_CHECK_LAUNCH("gather_add_rmsnorm");
     return 0;
 }

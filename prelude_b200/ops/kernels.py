@@ -62,36 +62,66 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
     return out
 
 
-def add_rmsnorm(x: Optional[torch.Tensor], res: torch.Tensor, weight: torch.Tensor, eps: float,
+class PartialSums:
+    """The output of a product whose K was cut into parts: ``parts`` is float32
+    [n, rows, width] and the value is their sum.  The residual add takes it as
+    it is and adds the parts up in float32; anyone else calls ``materialize``."""
+
+    def __init__(self, parts: torch.Tensor):
+        if parts.dim() != 3 or parts.dtype != torch.float32 or not parts.is_contiguous():
+            raise KernelLibraryError("PartialSums: a dense float32 [parts, rows, width] tensor is needed")
+        self.parts = parts
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    def materialize(self, dtype: torch.dtype) -> torch.Tensor:
+        return self.parts.sum(dim=0).to(dtype)
+
+
+def _x_args(x, out_dtype: torch.dtype, what: str):
+    """(pointer, parts, stride) of the addend of a fused add: a tensor of the run's type, partial sums, or nothing."""
+    if x is None:
+        return None, 0, 0
+    if isinstance(x, PartialSums):
+        _need(x.parts, what)
+        return x.parts.data_ptr(), x.parts.shape[0], x.parts.stride(0)
+    _need(x, what, out_dtype)
+    return x.data_ptr(), 0, 0
+
+
+def add_rmsnorm(x, res: torch.Tensor, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """res += x (when x is given); returns rmsnorm(res) * weight in ``out_dtype``."""
+    """res += x (when x is given: a tensor of ``out_dtype`` or ``PartialSums``); returns
+    rmsnorm(res) * weight in ``out_dtype``."""
     _need(res, "res", torch.float32)
     _need(weight, "weight", torch.float32)
     rows, width = res.shape
-    if x is not None:
-        _need(x, "x", out_dtype)
-        if x.shape != res.shape:
-            raise KernelLibraryError(f"add_rmsnorm: x {tuple(x.shape)} against residual {tuple(res.shape)}")
+    if x is not None and tuple(x.shape) != tuple(res.shape):
+        raise KernelLibraryError(f"add_rmsnorm: x {tuple(x.shape)} against residual {tuple(res.shape)}")
     if weight.numel() != width:
         raise KernelLibraryError(f"add_rmsnorm: weight has {weight.numel()} elements, rows have {width}")
+    ptr, parts, stride = _x_args(x, out_dtype, "x")
     if out is None:
         out = torch.empty((rows, width), dtype=out_dtype, device=res.device)
-    check(_l.library().pb_add_rmsnorm(_ptr(x), res.data_ptr(), weight.data_ptr(), out.data_ptr(),
+    check(_l.library().pb_add_rmsnorm(ptr, parts, stride, res.data_ptr(), weight.data_ptr(), out.data_ptr(),
                                       dtype_code(out_dtype), rows, width, float(eps), _stream()), "add_rmsnorm")
     return out
 
 
-def gather_add_rmsnorm(x: Optional[torch.Tensor], res: torch.Tensor, rows: torch.Tensor, weight: torch.Tensor,
+def gather_add_rmsnorm(x, res: torch.Tensor, rows: torch.Tensor, weight: torch.Tensor,
                        eps: float, out_dtype: torch.dtype) -> torch.Tensor:
     """rmsnorm(res[rows] + x[rows]) * weight for the chosen rows; res is not changed."""
     _need(res, "res", torch.float32)
     _need(rows, "rows", torch.int32)
     _need(weight, "weight", torch.float32)
-    if x is not None:
-        _need(x, "x", out_dtype)
+    if x is not None and tuple(x.shape) != tuple(res.shape):
+        raise KernelLibraryError(f"gather_add_rmsnorm: x {tuple(x.shape)} against residual {tuple(res.shape)}")
+    ptr, parts, stride = _x_args(x, out_dtype, "x")
     total, width = res.shape
     out = torch.empty((rows.numel(), width), dtype=out_dtype, device=res.device)
-    check(_l.library().pb_gather_add_rmsnorm(_ptr(x), res.data_ptr(), rows.data_ptr(), weight.data_ptr(),
+    check(_l.library().pb_gather_add_rmsnorm(ptr, parts, stride, res.data_ptr(), rows.data_ptr(), weight.data_ptr(),
                                              out.data_ptr(), dtype_code(out_dtype), rows.numel(), total, width,
                                              float(eps), _stream()), "gather_add_rmsnorm")
     return out

@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 class KernelLibraryError(RuntimeError):
@@ -27,9 +27,9 @@ _SIGNATURES = {
     "pb_built_for_sm": ([], I),
     "pb_check_device": ([], I),
     "pb_embed_gather": ([P, P, I, P, I, I, I, P], I),
-    "pb_add_rmsnorm": ([P, P, P, P, I, I, I, F, P], I),
+    "pb_add_rmsnorm": ([P, I, L, P, P, P, I, I, I, F, P], I),
     "pb_rmsnorm": ([P, P, P, I, I, I, F, P], I),
-    "pb_gather_add_rmsnorm": ([P, P, P, P, P, I, I, I, I, F, P], I),
+    "pb_gather_add_rmsnorm": ([P, I, L, P, P, P, P, I, I, I, I, F, P], I),
     "pb_qknorm_rope_kvwrite": ([P, P, P, L, P, P, P, I, P, P, F, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, I, P, P], I),
     "pb_paged_attention_ref": ([P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
     "pb_silu_mul": ([P, P, I, I, I, P], I),
@@ -44,7 +44,7 @@ _SIGNATURES = {
     "pb_attention_decode_blocks_per_sm": ([I], I),
     "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P], I),
     "pb_gemm_stream_supported": ([I, I, I, L, L], I),
-    "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, P, P], I),
+    "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, P, P], I),
     "pb_gemm_tc_supported": ([I, I, I, L, L], I),
     "pb_gemm_tc_scratch_bytes": ([I, I, I], L),
     "pb_gemm_tc_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, P, P, P], I),

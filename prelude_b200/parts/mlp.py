@@ -46,6 +46,8 @@ class GatedMlp:
         self.w_gate_up = torch.cat([mat("gate_proj.weight"), mat("up_proj.weight")], dim=0).contiguous()
         self.w_down = mat("down_proj.weight").contiguous()
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor):
+        """The feed-forward of x; what comes back goes to a fused residual add, which also takes
+        the partial sums of a product whose K was cut into parts."""
         gate_up = linear(x, self.w_gate_up)
-        return linear(_ACTIVATIONS[self.spec.activation](gate_up), self.w_down)
+        return linear(_ACTIVATIONS[self.spec.activation](gate_up), self.w_down, partial_sums_ok=True)

@@ -65,6 +65,52 @@ def test_add_rmsnorm(dtype, T, H, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("T,H,parts", [(8, 2560, 4), (3, 100, 2), (1, 64, 1), (5, 9000, 3), (7, 74, 5)])
+def test_add_rmsnorm_of_partial_sums(dtype, T, H, parts):
+    # the addend as float32 parts to be added up (a product whose K was cut): same result as adding their sum
+    from prelude_b200.ops.kernels import PartialSums
+    eps = 1e-5
+    p, res, w = rnd(parts, T, H, seed=4), rnd(T, H, seed=2), 1 + 0.3 * rnd(H, seed=3)
+    total = res.clone()
+    for i in range(parts):
+        total += p[i]
+    want = total / torch.sqrt((total * total).mean(-1, keepdim=True) + eps) * w
+    res2 = res.clone()
+    y = K().add_rmsnorm(PartialSums(p), res2, w, eps, dtype)
+    assert torch.equal(res2, total)                             # the parts in ascending order, in 32-bit
+    assert (y.float() - want).abs().max() <= tol(dtype, float(want.abs().max()))
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV)
+    yg = K().gather_add_rmsnorm(PartialSums(p), res, rows, w, eps, dtype)
+    assert (yg.float() - want[rows.long()]).abs().max() <= tol(dtype, float(want.abs().max()))
+    assert (PartialSums(p).materialize(torch.float32) - p.sum(0)).abs().max() == 0
+    with pytest.raises(Exception, match="against residual"):
+        K().add_rmsnorm(PartialSums(rnd(2, T, H + 4)), res2, w, eps, dtype)
+
+
+@pytest.mark.parametrize("splits", [2, 4])
+@pytest.mark.parametrize("M,N,K_", [(8, 2560, 9728), (3, 100, 8192), (16, 300, 4096)])
+def test_gemm_stream_partial_sums(M, N, K_, splits):
+    from prelude_b200.ops.linear import gemm_stream, linear, stream_splits
+    from prelude_b200.ops.kernels import PartialSums
+    x, w = rnd(M, K_, dtype=torch.bfloat16, seed=21), rnd(N, K_, dtype=torch.bfloat16, seed=22, scale=0.05)
+    want = x.double() @ w.double().T
+    parts = gemm_stream(x, w, splits=splits)
+    assert parts.shape == (splits, M, N) and parts.dtype == torch.float32
+    assert (parts.double().sum(0) - want).abs().max() <= 2e-3 * max(1.0, float(want.abs().max()))
+    # every part is the product over its own columns
+    kp = K_ // splits
+    for s in range(splits):
+        wp = x[:, s * kp:(s + 1) * kp].double() @ w[:, s * kp:(s + 1) * kp].double().T
+        assert (parts[s].double() - wp).abs().max() <= 2e-3 * max(1.0, float(wp.abs().max()))
+    got = linear(x, w, partial_sums_ok=True)
+    if stream_splits(M, N, K_) > 1:
+        assert isinstance(got, PartialSums) and got.parts.shape[0] == stream_splits(M, N, K_)
+    else:
+        assert isinstance(got, torch.Tensor)
+    assert isinstance(linear(x, w), torch.Tensor)               # never unless the caller says its reader can take them
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("T,I", [(1, 8), (13, 9728), (6, 200), (3, 37)])
 def test_silu_mul(dtype, T, I):
     gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)

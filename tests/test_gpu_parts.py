@@ -58,7 +58,10 @@ def test_feed_forward_part(dtype):
     part.load(_store(w).get, _ctx(dtype))
     x = torch.randn(11, H).to(dtype)
     want = plain.swiglu_mlp(x.float(), {k: v.float() for k, v in w.items()}, "m")
-    got = part.forward(x.to(DEV)).float().cpu()
+    got = part.forward(x.to(DEV))
+    if not isinstance(got, torch.Tensor):       # partial sums of a product whose K was cut into parts
+        got = got.materialize(dtype)
+    got = got.float().cpu()
     assert (got - want).abs().max() <= _tol(dtype, want)
     with pytest.raises(ValueError, match="activation"):
         make_part("feed_forward", GatedMlpSpec(H, I, activation="relu"), "m")
