@@ -8,12 +8,11 @@ bfloat16, float32 accumulation:
   * up to 16 rows (decode steps): the weight-streaming kernel of this library
     (bulk copies into a shared-memory ring that start before the previous kernel
     has finished, mma.sync, every block owning whole output features);
+  * cuBLAS through torch.mm above 16 rows, which is where the reference's own
+    dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433);
   * the tcgen05 kernel of this library (TMA, tensor memory, a persistent grid that
-    balances the stream of weight bytes over all blocks) for float32 outputs of
-    wider batches (the output head); PRELUDE_TC_GEMM=all sends every product
-    with more than 16 rows there;
-  * cuBLAS through torch.mm elsewhere, which is where the reference's own
-    dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433).
+    balances the stream of weight bytes over all blocks) when PRELUDE_TC_GEMM=all
+    asks for it: measured behind cuBLAS at every shape above 16 rows.
 """
 from __future__ import annotations
 
@@ -28,7 +27,7 @@ from .library import KernelLibraryError, check
 
 # rows up to which the streaming kernel is used (0 turns it off; it takes 16 at most)
 STREAM_MAX_ROWS = int(os.environ.get("PRELUDE_STREAM_MAX_ROWS", "16"))
-# which wider products go to the tcgen05 kernel: "auto" (where it is the fastest measured), "all", "none"
+# "all" sends the products of more than 16 rows to the tcgen05 kernel instead of cuBLAS
 TC_POLICY = os.environ.get("PRELUDE_TC_GEMM", "auto")
 
 _retired: List[torch.Tensor] = []          # outgrown buffers that captured graphs may still use
@@ -65,7 +64,6 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
 
 _tc_scratch: Dict[torch.device, torch.Tensor] = {}
 _tc_status: Dict[torch.device, torch.Tensor] = {}
-TC_DECODE_MAX_ROWS = 64        # up to this many rows a product counts as a decode step (a stream over the weights)
 
 
 def tc_status(device: torch.device) -> torch.Tensor:
@@ -112,13 +110,9 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] 
 
 
 def _tc_wanted(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> bool:
-    """Measured on B200 against cuBLAS: the tcgen05 kernel wins for the float32 output head
-    of a decode step; cuBLAS is ahead on the bfloat16 products of wide batches."""
-    if TC_POLICY == "all":
-        return True
-    if TC_POLICY == "none" or x.shape[0] > TC_DECODE_MAX_ROWS:
-        return False
-    return out_dtype == torch.float32
+    """Measured on B200 against cuBLAS, the tcgen05 kernel of this library is behind at every shape
+    that reaches this point (more than 16 rows), so it runs only when asked for."""
+    return TC_POLICY == "all"
 
 
 def stream_splits(M: int, N: int, Kdim: int) -> int:
