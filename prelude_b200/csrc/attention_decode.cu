@@ -39,6 +39,11 @@
 //    the block that arrives last for a (token, key/value head) adds the splits
 //    up in ascending order and writes the output.  The counters are left at
 //    zero for the next call.
+//  * All keys and values but the newest were written by earlier steps, so the
+//    loaders start the stream before the kernel that precedes this one on the
+//    stream (it writes q and the newest key and value) has finished, and wait
+//    for it only before the request's last tile; the consumers wait for it
+//    before they fetch q.
 //  * Waits on barriers are bounded in time: a warp that gives up raises the
 //    step's status word and goes on to the end.
 #include "attention_common.cuh"
@@ -121,20 +126,26 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
         const bool pages_in_smem = n_pages <= DEC_MAX_PAGES;
         if (pages_in_smem)
             for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) s_pages[i] = table[page_first + i];
-        // positions and block tables were written before the previous kernel started; q and the
-        // newest keys and values are that kernel's output
-        pb_grid_dep_wait();
-        // q rows of the group (rows from G on are zero)
+        __syncthreads();                                    // barriers and s_pages are ready
+        // Positions and block tables were written before this step's first kernel started, and so were all keys
+        // and values but the newest: the kernel before this one writes those (and q).  The loaders therefore
+        // start the stream at once and wait for that kernel only before the tile that holds the newest key; the
+        // consumers wait for it before they fetch q.
         const int chunks = d >> 3;
-        for (int c = threadIdx.x; c < 16 * chunks; c += DEC_THREADS) {
-            const int row = c / chunks, ch = c - row * chunks;
-            const bool ok = row < G;
-            const size_t src = ok ? (((size_t)tok * p.n_heads + kvh * G + row) * d + ch * 8) : 0;
-            cp_async16(sQ + row * QSTRIDE + ch * 8, p.q + src, ok);
+        const bool holds_newest = kt1 == kt_hi;             // this block's last tile is the request's last
+        if (warp < 4) {
+            pb_grid_dep_wait();
+            // q rows of the group (rows from G on are zero)
+            for (int c = threadIdx.x; c < 16 * chunks; c += 128) {
+                const int row = c / chunks, ch = c - row * chunks;
+                const bool ok = row < G;
+                const size_t src = ok ? (((size_t)tok * p.n_heads + kvh * G + row) * d + ch * 8) : 0;
+                cp_async16(sQ + row * QSTRIDE + ch * 8, p.q + src, ok);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");   // q is ready (the four consumer warps only)
         }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();                                    // barriers, s_pages and q are ready
 
         const int n_tiles = (kt1 - kt0 + 1) * (BN / BNW);   // consumer tiles of BNW keys; tile i belongs to warp i % NC
         const int key_base = kt0 * BN;
@@ -153,6 +164,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
 #pragma unroll 1
                 for (int i = 0; i < n_tiles; ++i) {
                     const int stage = i % S;
+                    if (holds_newest && i == n_tiles - 1) pb_grid_dep_wait();
                     ok = mbar_wait_bounded(&empty_bar[stage], ((i / S) & 1) ^ 1);
                     if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                     if (lane == 0) *(volatile int*)&s_issued = i + 1;       // the stage's previous tenant has been consumed
@@ -192,6 +204,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
 #pragma unroll 1
             for (int i = 0; i < n_tiles; ++i) {
                 const int stage = i % S;
+                if (holds_newest && i == n_tiles - 1) pb_grid_dep_wait();
                 ok = mbar_wait_bounded(&empty_bar[stage], ((i / S) & 1) ^ 1);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                 if (lt == 0) *(volatile int*)&s_issued = i + 1;             // the stage's previous tenant has been consumed
