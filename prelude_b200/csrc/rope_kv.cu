@@ -14,8 +14,12 @@
 // elements from rotary_dim on pass through.  cos/sin are float32 tables
 // [max_positions, rotary_dim/2].
 //
-// One warp per (token, head).  Norm weights and the tables may be null: no
-// norm, no rotation.  A page id outside [0, num_pages) is never written; the
+// One warp per (token, head) in the general kernel.  bfloat16 rows whose head
+// size is a power of two up to 256 take the vector kernel: 16 bytes per lane,
+// head_dim / 8 lanes per (token, head) and several of those per warp; the two
+// halves of a rotation pair sit in two lanes of the group and are exchanged by
+// a shuffle; every row is read once.  Norm weights and the tables may be null:
+// no norm, no rotation.  A page id outside [0, num_pages) is never written; the
 // kernel raises *status instead.
 #include "common.cuh"
 
@@ -100,6 +104,110 @@ __global__ void qknorm_rope_kvwrite_kernel(
     }
 }
 
+// The vector kernel: LANES = head_dim / 8 lanes per (token, head), 8 elements each.
+template <int LANES>
+__global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+    long long token_stride, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
+    __nv_bfloat16* __restrict__ v_pages, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int max_positions,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
+    const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
+    int n_tokens, int n_heads, int n_kv_heads, int write_kv, int swizzle, int* __restrict__ status) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    constexpr int D = LANES * 8;
+    const int heads_per_token = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;     // (token, head) of this lane
+    const int c = threadIdx.x % LANES;                                                       // its 16-byte chunk
+    const bool live = group < (long long)n_tokens * heads_per_token;
+    // lanes without a row keep going (the shuffles below are warp-wide) on row 0 and store nothing
+    const int t = live ? (int)(group / heads_per_token) : 0;
+    const int slot = live ? (int)(group % heads_per_token) : 0;
+    const int pos = positions[t];
+    const bool is_q = slot < n_heads, is_k = !is_q && slot < n_heads + n_kv_heads;
+    const int h = is_q ? slot : (is_k ? slot - n_heads : slot - n_heads - n_kv_heads);
+    const __nv_bfloat16* src = (is_q ? q : is_k ? k : v) + (size_t)t * token_stride + (size_t)h * D + c * 8;
+    __nv_bfloat16* dst = nullptr;
+    bool store = live;
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_heads + h) * D + c * 8;
+    } else {
+        const int seq = token_seq[t];
+        const int page = pos >= 0 ? block_table[(size_t)seq * table_stride + pos / page_size] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (live && c == 0 && status) atomicExch(status, 2);
+            store = false;
+        } else {
+            const int in_page = pos % page_size;
+            const int cc = swizzle ? (c ^ (in_page & 7)) : c;                                // chunks of a page row may be permuted
+            dst = (is_k ? k_pages : v_pages) + (((size_t)page * n_kv_heads + h) * page_size + in_page) * D + cc * 8;
+        }
+    }
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    if (!is_q && !is_k) {                                                                    // values: plain copy
+        if (store) *reinterpret_cast<uint4*>(dst) = raw;
+        // no return: the lanes of this warp that hold q or k rows need all lanes at the shuffles
+    }
+    float x[8];
+    {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h2[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+    }
+    const float* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);       // over the lanes of the row
+    if (weight != nullptr) {
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        const float4 w0 = *reinterpret_cast<const float4*>(weight + c * 8), w1 = *reinterpret_cast<const float4*>(weight + c * 8 + 4);
+        x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
+        x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
+    }
+    // rotation: element j of the first half pairs with j + half; the partner chunk sits half / 8 lanes away
+    const int half = (cos_table != nullptr) ? rotary_dim / 2 : 0;
+    const int hc = half / 8;                                                                 // chunks per half (0: no rotation)
+    const bool first = c < hc, second = c >= hc && c < 2 * hc;
+    const int partner = first ? c + hc : (second ? c - hc : c);
+    const int src_lane = (threadIdx.x & 31) - c + partner;
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = __shfl_sync(0xffffffffu, x[i], src_lane);
+    if ((first || second) && (is_q || is_k)) {
+        if (pos < 0 || pos >= max_positions) {
+            if (live && c == 0 && status) atomicExch(status, 3);
+            store = false;
+        } else {
+            const int j0 = (first ? c : c - hc) * 8;
+            const float* cp = cos_table + (size_t)pos * half + j0;
+            const float* sp = sin_table + (size_t)pos * half + j0;
+            const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = first ? x[i] * cs[i] - y[i] * sn[i] : x[i] * cs[i] + y[i] * sn[i];
+        }
+    }
+    if (store && (is_q || is_k)) {
+        uint4 out;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+        *reinterpret_cast<uint4*>(dst) = out;
+    }
+}
+
+template <int LANES, typename... Args>
+static void launch_rope_vec(long long rows, cudaStream_t stream, Args... args) {
+    const int threads = 256;
+    const long long blocks = (rows * LANES + threads - 1) / threads;
+    pb_launch(qknorm_rope_kvwrite_vec_kernel<LANES>, dim3((unsigned)blocks), dim3(threads), 0, stream, args...);
+}
+
 PB_API int pb_qknorm_rope_kvwrite(
     const void* q, const void* k, const void* v, long long token_stride, void* q_out, void* k_pages, void* v_pages,
     int dtype, const float* q_weight, const float* k_weight, float eps, const float* cos_table,
@@ -116,6 +224,31 @@ PB_API int pb_qknorm_rope_kvwrite(
                    "qknorm_rope_kvwrite: cache write asked for without cache arguments");
     if (n_tokens == 0) return 0;
     long long warps = (long long)n_tokens * (n_heads + (write_kv ? 2 * n_kv_heads : 0));
+    // the vector kernel: bfloat16, a power-of-two head size from 16 to 256, rotation halves of whole 16-byte
+    // chunks, everything 16-byte aligned
+    const bool pow2 = head_dim >= 16 && head_dim <= 256 && (head_dim & (head_dim - 1)) == 0;
+    const bool rot_ok = cos_table == nullptr || rotary_dim % 16 == 0;
+    const bool aligned = pb_aligned(q, 16) && pb_aligned(q_out, 16) && token_stride % 8 == 0 &&
+                         (!write_kv || (pb_aligned(k, 16) && pb_aligned(v, 16) && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16))) &&
+                         (q_weight == nullptr || pb_aligned(q_weight, 16)) && (k_weight == nullptr || pb_aligned(k_weight, 16)) &&
+                         (cos_table == nullptr || (pb_aligned(cos_table, 16) && pb_aligned(sin_table, 16) && (rotary_dim / 2) % 4 == 0));
+    if (dtype == PB_BF16 && pow2 && rot_ok && aligned && warps * (head_dim / 8) < (1ll << 38)) {
+        typedef const __nv_bfloat16* CB;
+        typedef __nv_bfloat16* B;
+#define PB_ROPE_VEC(L)                                                                                                  \
+        launch_rope_vec<L>(warps, stream, (CB)q, (CB)k, (CB)v, token_stride, (B)q_out, (B)k_pages, (B)v_pages, q_weight,   \
+                           k_weight, eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq,           \
+                           block_table, table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, write_kv,        \
+                           swizzle, status)
+        if (head_dim == 16) PB_ROPE_VEC(2);
+        else if (head_dim == 32) PB_ROPE_VEC(4);
+        else if (head_dim == 64) PB_ROPE_VEC(8);
+        else if (head_dim == 128) PB_ROPE_VEC(16);
+        else PB_ROPE_VEC(32);
+#undef PB_ROPE_VEC
+        PB_CHECK_LAUNCH("qknorm_rope_kvwrite");
+        return 0;
+    }
     const int threads = 256;
     long long blocks = (warps * 32 + threads - 1) / threads;
     PB_REQUIRE(blocks < (1ll << 31), "qknorm_rope_kvwrite: too many rows");

@@ -250,7 +250,8 @@ def test_attention_finds_the_one_key_that_matters(dtype, where):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("nH,nKV,D,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 1, 48, 48), (8, 2, 128, 128),
-                                          (3, 3, 80, 32), (2, 1, 256, 256), (2, 2, 64, 0)])
+                                          (3, 3, 80, 32), (2, 1, 256, 256), (2, 2, 64, 0), (4, 2, 128, 64),
+                                          (4, 4, 64, 32), (2, 1, 128, 24), (32, 8, 128, 128), (3, 1, 32, 16)])
 @pytest.mark.parametrize("norm", [True, False])
 def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
     T, page, num_pages, eps, theta = 11, 8, 9, 1e-5, 10000.0
