@@ -19,6 +19,7 @@ REQUESTS = {
     "A": {"a1": 1, "a5": 5, "a17": 17, "a70": 70},
     "B": {"b2": 2, "b9": 9, "b31": 31, "b64": 64, "b150": 150},
     "C": {"c40": 40, "c33": 33, "c129": 129},
+    "D": {"d3": 3, "d70": 70, "d200": 200},
 }
 
 
@@ -55,14 +56,14 @@ def _runner(folder, dtype, page_size, num_pages):
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
-    for which in "ABC":
+    for which in "ABCD":
         for dtype in (torch.float32, torch.bfloat16):
             out[(which, dtype)] = tiny.make_folder(root, which, dtype)
     return out
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
 def test_cuts_match_plain(folders, which, dtype, cut):
     folder = folders[(which, dtype)]
@@ -108,6 +109,7 @@ def test_bf16_with_every_product_on_the_tcgen05_kernel(folders, monkeypatch, whi
     library's own tensor-core product instead of cuBLAS."""
     from prelude_b200.ops import linear
     monkeypatch.setattr(linear, "TC_POLICY", "all")
+    monkeypatch.setattr(linear, "STREAM_MAX_ROWS", 0)           # decode steps too
     folder = folders[(which, torch.bfloat16)]
     reqs = _requests(which)
     ref = _reference(which, folder, reqs)

@@ -25,7 +25,15 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               max_position_embeddings=1024, rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=True,
               attention_bias=True)
 
+# the sizes at which the fast kernels take their special paths: head size 128 (permuted pages, bulk copies, the
+# vector rope kernel), a feed-forward so wide that the down projection of a decode step cuts K into parts
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=500, hidden_size=192,
+              intermediate_size=8192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+              max_position_embeddings=512, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+              attention_bias=False, use_sliding_window=False, hidden_act="silu")
+
 PARAMS = {"A": (TINY_A, dict(seed=0, std=0.02, norm_jitter=0.1), 4),
+          "D": (TINY_D, dict(seed=3, std=0.02, norm_jitter=0.1), 16),
           "B": (TINY_B, dict(seed=1, std=0.03, norm_jitter=0.2), 8),
           "C": (TINY_C, dict(seed=2, std=0.05, norm_jitter=0.3), 16)}
 
