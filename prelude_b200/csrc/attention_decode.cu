@@ -402,18 +402,67 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    const int ns = p.n_splits;
+    const size_t th0 = (size_t)tok * p.n_heads + kvh * G;
+    if (ns <= 64) {
+        // Every load below is issued before its value is needed, so the merge costs a few trips to the L2 cache and
+        // not one per split.  Maximum and sum of every split into shared memory; one warp per row turns them into
+        // the weight of each split; then every output element adds its splits up in ascending order.
+        float* sMs = sL + 64;                               // [G][64] maxima, then [G][64] sums, then [G] 1 / total
+        float* sLs = sMs + 16 * 64;
+        float* sInv = sLs + 16 * 64;
+        for (int idx = threadIdx.x; idx < G * ns; idx += DEC_THREADS) {
+            const int row = idx / ns, sp = idx - row * ns;
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((th0 + row) * ns + sp) * 2));
+            sMs[row * 64 + sp] = v.x;
+            sLs[row * 64 + sp] = v.y;
+        }
+        __syncthreads();
+        for (int row = warp; row < G; row += DEC_THREADS / 32) {
+            float mm = -INFINITY;
+            for (int sp = lane; sp < ns; sp += 32) mm = fmaxf(mm, sMs[row * 64 + sp]);
+            mm = pb_warp_max(mm);
+            // the sum over the splits in ascending order, by one lane: the splits are few
+            float ls = 0.f;
+            for (int sp = lane; sp < ns; sp += 32) {
+                const float ms = sMs[row * 64 + sp];
+                sMs[row * 64 + sp] = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);   // the split's weight
+            }
+            __syncwarp();
+            if (lane == 0) {
+                for (int sp = 0; sp < ns; ++sp) ls += sMs[row * 64 + sp] * sLs[row * 64 + sp];
+                sInv[row] = ls > 0.f ? 1.0f / ls : 0.f;
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < G * d; idx += DEC_THREADS) {
+            const int row = idx / d, col = idx - row * d;
+            const float* po = p.part_o + (th0 + row) * ns * d + col;
+            float acc = 0.f;
+            for (int s0 = 0; s0 < ns; s0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = (s0 + u < ns) ? __ldcg(po + (size_t)(s0 + u) * d) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (s0 + u < ns) acc += sMs[row * 64 + s0 + u] * v[u];
+            }
+            p.out[(th0 + row) * d + col] = __float2bfloat16_rn(acc * sInv[row]);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < G * d; idx += DEC_THREADS) {
         const int row = idx / d, col = idx - row * d;
-        const size_t th = (size_t)tok * p.n_heads + kvh * G + row;
-        const float* ml = p.part_ml + th * p.n_splits * 2;
+        const size_t th = th0 + row;
+        const float* ml = p.part_ml + th * ns * 2;
         float mm = -INFINITY;
-        for (int s = 0; s < p.n_splits; ++s) mm = fmaxf(mm, __ldcg(ml + 2 * s));
+        for (int s = 0; s < ns; ++s) mm = fmaxf(mm, __ldcg(ml + 2 * s));
         float acc = 0.f, ls = 0.f;
-        for (int s = 0; s < p.n_splits; ++s) {
+        for (int s = 0; s < ns; ++s) {
             const float ms = __ldcg(ml + 2 * s);
             const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
             ls += f * __ldcg(ml + 2 * s + 1);
-            acc += f * __ldcg(p.part_o + (th * p.n_splits + s) * d + col);
+            acc += f * __ldcg(p.part_o + (th * ns + s) * d + col);
         }
         p.out[th * d + col] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
     }
@@ -422,7 +471,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
 template <int DMAX, bool BULK> static size_t decode_smem() {
     using T = DecodeTiling<DMAX, BULK>;
     size_t tiles = (size_t)T::STAGES * T::STAGE_ELEMS * 2 + (size_t)16 * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
-    size_t merge = (size_t)(4 * 16 * DMAX + 128) * 4;
+    size_t merge = (size_t)(4 * 16 * DMAX + 128 + 2 * 16 * 64 + 16) * 4;   // the warps' partial results, then the splits' maxima and sums
     return tiles > merge ? tiles : merge;
 }
 
