@@ -90,9 +90,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
     constexpr int S = T::STAGES, NC = T::NC;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    constexpr int QSTRIDE = DMAX + 8;
+    using TG = AttnTileGeom<DMAX, BULK>;                     // q rows are laid out like key rows: padded, or dense with permuted chunks
+    constexpr int QSTRIDE = TG::STRIDE;
     __nv_bfloat16* sQ = stages + S * T::STAGE_ELEMS;
-    int32_t* s_pages = reinterpret_cast<int32_t*>(sQ + 16 * QSTRIDE);
+    int32_t* s_pages = reinterpret_cast<int32_t*>(sQ + 16 * (DMAX + 8));
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S];
     __shared__ int s_last, s_issued;
 
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
                 const int row = c / chunks, ch = c - row * chunks;
                 const bool ok = row < G;
                 const size_t src = ok ? (((size_t)tok * p.n_heads + kvh * G + row) * d + ch * 8) : 0;
-                cp_async16(sQ + row * QSTRIDE + ch * 8, p.q + src, ok);
+                cp_async16(sQ + row * QSTRIDE + (BULK ? (ch ^ (row & 7)) : ch) * 8, p.q + src, ok);
             }
             cp_async_commit();
             cp_async_wait<0>();
@@ -237,6 +238,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
             cp_async_wait<0>();                             // nothing of this thread is in flight when shared memory changes its use
         } else {
             // ---------------- consumers: warp w takes tiles w, w + NC, ... ----------------
+            FragOffsets<DMAX, BULK> frag;
+            attn_frag_offsets<DMAX, BULK>(frag, 0, lane);
+            const unsigned sQ_a = smem_u32(sQ);
+            const int row_pos[2] = {pos, pos};              // every row of the tile is a head of the one new token
 #pragma unroll 1
             for (int i = warp; warp < NC && i < n_tiles; i += NC) {
                 const int stage = i % S;
@@ -254,25 +259,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
                 const __nv_bfloat16* sK = stages + stage * T::STAGE_ELEMS;
                 const __nv_bfloat16* sV = sK + BNW * STRIDE;
                 const int key0 = key_base + i * BNW;
-                constexpr int NT = BNW / 8;
-                float s[NT][4];
-#pragma unroll
-                for (int q = 0; q < NT; ++q) s[q][0] = s[q][1] = s[q][2] = s[q][3] = 0.f;
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {
-                    if (kk * 16 < d) {
-                        unsigned a[4];
-                        ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (lane & 15) * QSTRIDE + kk * 16 + (lane >> 4) * 8);
-#pragma unroll
-                        for (int n2 = 0; n2 < NT / 2; ++n2) {
-                            unsigned b0, b1, b2, b3;
-                            const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7);
-                            ldmatrix_x4(b0, b1, b2, b3, tile_at(sK, key, kk * 2 + ((lane >> 3) & 1)));
-                            mma_bf16(s[2 * n2], a, b0, b1);
-                            mma_bf16(s[2 * n2 + 1], a, b2, b3);
-                        }
-                    }
-                }
                 const bool edge = key0 < lo || key0 + BNW - 1 > pos;         // some key of the tile is not visible
                 if (BULK && edge) {
                     // value rows that no visible key stands for hold whatever the page (or the stage) held:
@@ -286,59 +272,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
                     fence_proxy_async();                    // these ordinary stores come before the bulk copy that refills the stage
                     __syncwarp();
                 }
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
-                        s[nt][e] = (!edge || (j >= lo && j <= pos)) ? s[nt][e] * p.scale_log2 : -INFINITY;
-                    }
-                }
-                float corr[2], mref[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    float rmax = -INFINITY;
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) rmax = fmaxf(rmax, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
-                    rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
-                    rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
-                    const float m_new = fmaxf(m[h], rmax);
-                    corr[h] = (m[h] == m_new) ? 1.f : ((m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new));
-                    mref[h] = (m_new == -INFINITY) ? 0.f : m_new;
-                    m[h] = m_new;
-                    l[h] *= corr[h];
-                }
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float pv = exp2f(s[nt][e] - mref[e >> 1]);
-                        s[nt][e] = pv;
-                        l[e >> 1] += pv;
-                    }
-                }
-                // the accumulator is rescaled only when some row's maximum moved
-                if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
-#pragma unroll
-                    for (int q = 0; q < DMAX / 8; ++q) {
-                        o[q][0] *= corr[0]; o[q][1] *= corr[0]; o[q][2] *= corr[1]; o[q][3] *= corr[1];
-                    }
-                }
-#pragma unroll
-                for (int ks = 0; ks < BNW / 16; ++ks) {
-                    unsigned a[4] = {pack_bf16(s[2 * ks][0], s[2 * ks][1]), pack_bf16(s[2 * ks][2], s[2 * ks][3]),
-                                     pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]), pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3])};
-#pragma unroll
-                    for (int d2 = 0; d2 < KSTEPS; ++d2) {
-                        if (d2 * 16 < d) {
-                            unsigned b0, b1, b2, b3;
-                            const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-                            ldmatrix_x4_trans(b0, b1, b2, b3, tile_at(sV, key, d2 * 2 + (lane >> 4)));
-                            mma_bf16(o[2 * d2], a, b0, b1);
-                            mma_bf16(o[2 * d2 + 1], a, b2, b3);
-                        }
-                    }
-                }
+                attn_tile<DMAX, BULK>(o, m, l, frag, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, edge, p.window,
+                                      p.scale_log2, t4);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[stage]);               // the stage may be refilled
             }
@@ -535,7 +470,8 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
         if ((1 << s) == page_size) dp.page_shift = s;
     // bulk copies bring whole runs of a page: a run must tile the 64-key tile evenly and start at a multiple
     // of 8 tokens (the rows then sit at the row numbers their permutation was made for)
-    const bool bulk = swizzle && page_size % 8 == 0 && (BNW % page_size == 0 || page_size % BNW == 0);
+    const bool bulk = swizzle && page_size % 8 == 0 && (BNW % page_size == 0 || page_size % BNW == 0) &&
+                      (head_dim == 64 || head_dim == 128 || head_dim == 256);    // the dense layout has no room for a narrower head
     int e = bulk ? (head_dim <= 64 ? launch_decode<64, true>(dp, stream)
                     : head_dim <= 128 ? launch_decode<128, true>(dp, stream) : launch_decode<256, true>(dp, stream))
                  : (head_dim <= 64 ? launch_decode<64, false>(dp, stream)

@@ -34,33 +34,8 @@
 // relative to a slightly stale maximum, which the final division cancels).
 #include "attention_common.cuh"
 
-#include <type_traits>
-
 #define PF_ROWS 64              // rows of a block's tile
 #define PF_COMPUTE_THREADS 128
-#define PF_RESCALE_STEP 8.0f    // log2 of the growth of a row maximum that forces a rescale
-
-template <int I, int N, typename F> __device__ __forceinline__ void static_for(F&& f) {
-    if constexpr (I < N) {
-        f(std::integral_constant<int, I>{});
-        static_for<I + 1, N>(f);
-    }
-}
-
-// ldmatrix from a shared-memory byte address plus a compile-time offset
-template <int IMM> __device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(IMM));
-}
-template <int IMM> __device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(IMM));
-}
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
 
 template <int DMAX, bool BULK> struct PrefillTiling {
     static constexpr int STRIDE = BULK ? DMAX : DMAX + 8;     // elements per row in shared memory
@@ -72,161 +47,12 @@ template <int DMAX, bool BULK> struct PrefillTiling {
     static constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES;
     static constexpr int THREADS = BULK ? PF_COMPUTE_THREADS + 32 : PF_COMPUTE_THREADS;
     static constexpr int BLOCKS_PER_SM = (2 * (SMEM_BYTES + 1024) <= 227 * 1024) ? 2 : 1;
-    // ldmatrix row addresses: with permuted chunks, chunk c of row r sits at c ^ (r & 7).  The chunk
-    // index of step kk is 2 kk + b with a per-lane bit b, and r & 7 = lane & 7, so the position is
-    // (2 kk) ^ x with the per-lane constant x = b ^ (lane & 7): four distinct values of the low bits
-    // (kk & 3), kept in registers, and bit 3 of the chunk (kk >> 2), an immediate.
-    static constexpr int NOFF = BULK ? 4 : 1;
 };
 
 struct PrefillParams {
     AttnParams a;
     int page_shift;             // log2(page_size) when it is a power of two, else -1
 };
-
-// What a compute thread keeps about its place in the fragments.
-template <int DMAX, bool BULK> struct FragOffsets {
-    unsigned q[PrefillTiling<DMAX, BULK>::NOFF], k[PrefillTiling<DMAX, BULK>::NOFF], v[PrefillTiling<DMAX, BULK>::NOFF];
-};
-
-template <int DMAX, bool BULK, int KK> __device__ __forceinline__ constexpr int step_imm() {
-    // byte offset of 16-element step KK beyond the per-lane offset that serves it
-    return BULK ? (KK >> 2) * 128 : KK * 32;
-}
-
-// One 64-key tile against this warp's 16 rows.
-template <int DMAX, bool BULK>
-__device__ __forceinline__ void prefill_tile(float (&o)[DMAX / 8][4], float (&m)[2], float (&l)[2],
-                                             const FragOffsets<DMAX, BULK>& f, unsigned sQ, unsigned sK, unsigned sV,
-                                             int d, int key0, const int (&row_pos)[2], bool edge, int window,
-                                             float scale_log2, int t4) {
-    using T = PrefillTiling<DMAX, BULK>;
-    constexpr int KSTEPS = DMAX / 16;
-    constexpr bool PIPE = DMAX <= 128;        // larger heads leave no registers for fragments fetched ahead
-
-    // ---- S = Q K^T: 16 rows x 64 keys; the fragments of the next 16-element step are fetched ahead ----
-    float s[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-    {
-        unsigned qa[PIPE ? 2 : 1][4], kb[PIPE ? 2 : 1][4][4];
-        unsigned kaddr[T::NOFF], qaddr[T::NOFF];
-#pragma unroll
-        for (int j = 0; j < T::NOFF; ++j) { kaddr[j] = sK + f.k[j]; qaddr[j] = sQ + f.q[j]; }
-        auto fetch = [&](auto kk_c, int buf) {
-            constexpr int kk = decltype(kk_c)::value;
-            constexpr int imm = step_imm<DMAX, BULK, kk>();
-            ldsm_x4<imm>(qa[buf], qaddr[BULK ? (kk & 3) : 0]);
-            static_for<0, 4>([&](auto n2_c) {
-                constexpr int n2 = decltype(n2_c)::value;
-                ldsm_x4<imm + n2 * 16 * T::ROW_BYTES>(kb[buf][n2], kaddr[BULK ? (kk & 3) : 0]);
-            });
-        };
-        if (PIPE) fetch(std::integral_constant<int, 0>{}, 0);
-        static_for<0, KSTEPS>([&](auto kk_c) {
-            constexpr int kk = decltype(kk_c)::value;
-            constexpr int buf = PIPE ? (kk & 1) : 0;
-            if (BULK || kk * 16 < d) {
-                if constexpr (!PIPE) fetch(kk_c, 0);
-                else if constexpr (kk + 1 < KSTEPS) {
-                    if (BULK || (kk + 1) * 16 < d) fetch(std::integral_constant<int, kk + 1>{}, buf ^ 1);
-                }
-#pragma unroll
-                for (int n2 = 0; n2 < 4; ++n2) {
-                    mma_bf16_free(s[2 * n2], qa[buf], kb[buf][n2][0], kb[buf][n2][1]);
-                    mma_bf16_free(s[2 * n2 + 1], qa[buf], kb[buf][n2][2], kb[buf][n2][3]);
-                }
-            }
-        });
-    }
-
-    // ---- mask (only in tiles with an invisible key), running maximum ----
-    if (edge) {
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
-                const int pr = row_pos[e >> 1];
-                const bool vis = j <= pr && (window <= 0 || j > pr - window);
-                s[nt][e] = vis ? s[nt][e] : -INFINITY;
-            }
-        }
-    }
-    float rmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-        rmax[0] = fmaxf(rmax[0], fmaxf(s[nt][0], s[nt][1]));
-        rmax[1] = fmaxf(rmax[1], fmaxf(s[nt][2], s[nt][3]));
-    }
-    bool grow = false;
-    float cand[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
-        rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
-        cand[h] = fmaxf(m[h], rmax[h] * scale_log2);          // scale > 0: the maximum commutes with it
-        grow = grow || cand[h] > m[h] + PF_RESCALE_STEP;      // also true for -inf -> finite
-    }
-    if (__any_sync(0xffffffffu, grow)) {
-        float corr[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            corr[h] = (m[h] == -INFINITY) ? 0.f : ex2_approx(m[h] - cand[h]);   // cand >= m; both -inf: nothing summed yet
-            m[h] = cand[h];
-            l[h] *= corr[h];
-        }
-#pragma unroll
-        for (int i = 0; i < DMAX / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
-        }
-    }
-    // exp2(s * scale - m); a row that has seen nothing yet has m = -inf and only -inf scores: exp2(-inf - 0) = 0
-    const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float pv = ex2_approx(fmaf(s[nt][e], scale_log2, -mref[e >> 1]));
-            s[nt][e] = pv;
-            l[e >> 1] += pv;
-        }
-    }
-
-    // ---- O += P V: 4 key steps x KSTEPS dim steps, one ldmatrix and two products each, fetched two steps ahead ----
-    {
-        unsigned pa[4][4];
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            pa[ks][0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-            pa[ks][1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-            pa[ks][2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-            pa[ks][3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-        }
-        unsigned vaddr[T::NOFF];
-#pragma unroll
-        for (int j = 0; j < T::NOFF; ++j) vaddr[j] = sV + f.v[j];
-        constexpr int TOTAL = 4 * KSTEPS, AHEAD = PIPE ? 2 : 0;
-        unsigned vb[PIPE ? 3 : 1][4];
-        auto fetch_v = [&](auto t_c) {
-            constexpr int t = decltype(t_c)::value;
-            constexpr int ks = t / KSTEPS, d2 = t % KSTEPS;
-            if (BULK || d2 * 16 < d)
-                ldsm_x4_trans<step_imm<DMAX, BULK, d2>() + ks * 16 * T::ROW_BYTES>(vb[PIPE ? t % 3 : 0], vaddr[BULK ? (d2 & 3) : 0]);
-        };
-        static_for<0, AHEAD>([&](auto t_c) { fetch_v(t_c); });
-        static_for<0, TOTAL>([&](auto t_c) {
-            constexpr int t = decltype(t_c)::value;
-            constexpr int ks = t / KSTEPS, d2 = t % KSTEPS;
-            if constexpr (t + AHEAD < TOTAL || AHEAD == 0) fetch_v(std::integral_constant<int, t + AHEAD>{});
-            if (BULK || d2 * 16 < d) {
-                constexpr int b = PIPE ? t % 3 : 0;
-                mma_bf16_free(o[2 * d2], pa[ks], vb[b][0], vb[b][1]);
-                mma_bf16_free(o[2 * d2 + 1], pa[ks], vb[b][2], vb[b][3]);
-            }
-        });
-    }
-}
 
 __device__ __forceinline__ void pf_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
@@ -374,18 +200,7 @@ attn_prefill_kernel(PrefillParams pp) {
     const int wp_min = pos0 + tok0 + tl_first, wp_max = pos0 + tok0 + min(tl_last, n_tok - 1);
 
     FragOffsets<DMAX, BULK> f;
-    {
-        const int x = lane & 7;
-        const int q_row = warp * 16 + (lane & 15), q_b = lane >> 4;
-        const int k_row = (lane >> 4) * 8 + x, k_b = (lane >> 3) & 1;
-        const int v_row = ((lane >> 3) & 1) * 8 + x, v_b = lane >> 4;
-#pragma unroll
-        for (int j = 0; j < T::NOFF; ++j) {
-            f.q[j] = q_row * T::ROW_BYTES + (BULK ? (((2 * j) ^ (q_b ^ x)) << 4) : q_b * 16);
-            f.k[j] = k_row * T::ROW_BYTES + (BULK ? (((2 * j) ^ (k_b ^ x)) << 4) : k_b * 16);
-            f.v[j] = v_row * T::ROW_BYTES + (BULK ? (((2 * j) ^ (v_b ^ x)) << 4) : v_b * 16);
-        }
-    }
+    attn_frag_offsets<DMAX, BULK>(f, warp * 16, lane);
     const unsigned sQ_a = smem_u32(sQ);
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -433,7 +248,7 @@ attn_prefill_kernel(PrefillParams pp) {
                     fence_proxy_async();                   // these ordinary stores come before the bulk copy that refills the stage
                     __syncwarp();
                 }
-                prefill_tile<DMAX, BULK>(o, m, l, f, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, tile_edge(key0),
+                attn_tile<DMAX, BULK>(o, m, l, f, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, tile_edge(key0),
                                          p.window, p.scale_log2, t4);
             }
             __syncwarp();
@@ -461,7 +276,7 @@ attn_prefill_kernel(PrefillParams pp) {
             __syncthreads();
             const int key0 = (kt0 + i) * BN;
             if (!tile_unseen(key0))
-                prefill_tile<DMAX, BULK>(o, m, l, f, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, tile_edge(key0),
+                attn_tile<DMAX, BULK>(o, m, l, f, sQ_a, smem_u32(sK), smem_u32(sV), d, key0, row_pos, tile_edge(key0),
                                          p.window, p.scale_log2, t4);
             __syncthreads();
         }
