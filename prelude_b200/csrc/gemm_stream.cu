@@ -30,6 +30,12 @@
 //    works on its columns of W and x only and writes float32 partial sums of
 //    its own, and whoever reads the output adds the parts (the residual add
 //    does).  Nothing waits for anything.
+//  * The gated form serves a feed-forward's merged gate and up projection: W
+//    holds the N gate rows, then the N up rows; a tile is 8 features, its first
+//    stage their gate rows and its second their up rows, so the two halves of
+//    the tensor-core tile are gate and up of the same features and the
+//    epilogue writes silu(gate) * up (float32 sums, one rounding) - the
+//    activation costs no kernel and the 2N-wide intermediate never exists.
 //  * Waits on barriers are bounded in time; a warp that gives up raises the
 //    status word and the block goes on to its end.
 // The tensor-memory kernel (gemm_tc.cu) is the wrong tool here: its instruction
@@ -63,6 +69,7 @@ struct GsParams {
     int stages;
     int out_f32;
     long long split_stride; // elements between the partial outputs of the splits of K (gridDim.y of them)
+    int gated;              // W holds N gate rows, then N up rows; the output is silu(gate) * up, N wide
     int* status;
 };
 
@@ -106,7 +113,8 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
     // This block's features, in tiles of 16 = two stages of 8 (the last tile may have one).  Loader and compute
     // warps walk the stages in the same order: tile, chunk of K, half.
     const int r0 = (int)((long long)blockIdx.x * p.N / gridDim.x), r1 = (int)((long long)(blockIdx.x + 1) * p.N / gridDim.x);
-    const int n_tiles = (r1 - r0 + 15) / 16;
+    const int span = p.gated ? GS_ROWS : 16;                   // features per tile
+    const int n_tiles = (r1 - r0 + span - 1) / span;
 
     if (threadIdx.x == 0) {
         s_issued = 0;
@@ -136,7 +144,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
         };
 #pragma unroll 1
         for (int tile = 0; tile < n_tiles && ok; ++tile) {
-            const int halves = (r1 - (r0 + tile * 16) > GS_ROWS) ? 2 : 1;
+            const int halves = (p.gated || r1 - (r0 + tile * span) > GS_ROWS) ? 2 : 1;
 #pragma unroll 1
             for (int kc = 0; kc < p.n_chunks && ok; ++kc) {
                 for (int h = 0; h < halves; ++h, ++i) {
@@ -144,9 +152,10 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
                     ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1);
                     if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                     if (lw == 0 && lane == 0) *(volatile int*)&s_issued = i + 1;   // the stage's previous tenant has been consumed
-                    const int row0 = r0 + tile * 16 + h * GS_ROWS;
+                    const int feat0 = r0 + tile * span + (p.gated ? 0 : h * GS_ROWS);   // first feature of the stage
+                    const int row0 = feat0 + (p.gated ? h * p.N : 0);                 // its row of W: up rows follow the gate rows
                     const int k0 = kc * p.ks, len = min(p.ks, p.K - k0);
-                    const int n_rows = min(GS_ROWS, r1 - row0);
+                    const int n_rows = min(GS_ROWS, r1 - feat0);
                     const int mine = min(PER, max(0, n_rows - lw * PER));        // rows of this stage that this warp brings
                     if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], (unsigned)mine * len * 2);
                     __syncwarp();
@@ -184,7 +193,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
     int stage = 0, phase = 0, item = 0;
 #pragma unroll 1
     for (int tile = 0; tile < n_tiles; ++tile) {
-        const int halves = (r1 - (r0 + tile * 16) > GS_ROWS) ? 2 : 1;
+        const int halves = (p.gated || r1 - (r0 + tile * span) > GS_ROWS) ? 2 : 1;
         // GS_CHAINS independent chains of sums, so that a product does not wait for the one before it
         float acc[GS_CHAINS][MT][4];
 #pragma unroll
@@ -253,16 +262,35 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
             }
         gs_bar_compute();
         if (*(volatile int*)&s_dead) return;
-        for (int idx = threadIdx.x; idx < p.M * 16; idx += GS_WARPS * 32) {
-            const int m = idx >> 4, rr = idx & 15;
-            const int n = r0 + tile * 16 + rr;
-            if (n < r1) {
-                float v = 0.f;
+        if (p.gated) {
+            // rows 0..7 of the tile are the gate sums of 8 features, rows 8..15 the up sums of the same features
+            for (int idx = threadIdx.x; idx < p.M * GS_ROWS; idx += GS_WARPS * 32) {
+                const int m = idx >> 3, rr = idx & 7;
+                const int n = r0 + tile * GS_ROWS + rr;
+                if (n < r1) {
+                    float gsum = 0.f, usum = 0.f;
 #pragma unroll
-                for (int w = 0; w < GS_WARPS; ++w) v += red[(size_t)w * 16 * 8 * MT + idx];
-                if (p.bias) v += p.bias[n];
-                if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-                else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+                    for (int w = 0; w < GS_WARPS; ++w) {
+                        gsum += red[(size_t)w * 16 * 8 * MT + m * 16 + rr];
+                        usum += red[(size_t)w * 16 * 8 * MT + m * 16 + rr + 8];
+                    }
+                    const float v = gsum / (1.0f + expf(-gsum)) * usum;
+                    if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+                    else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+                }
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < p.M * 16; idx += GS_WARPS * 32) {
+                const int m = idx >> 4, rr = idx & 15;
+                const int n = r0 + tile * 16 + rr;
+                if (n < r1) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < GS_WARPS; ++w) v += red[(size_t)w * 16 * 8 * MT + idx];
+                    if (p.bias) v += p.bias[n];
+                    if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+                    else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+                }
             }
         }
         gs_bar_compute();                                      // the sums are read before the next tile overwrites them
@@ -315,11 +343,13 @@ PB_API int pb_gemm_stream_supported(int M, int N, int K, long long ldw, long lon
     return gs_plan(M, K, &ks, &nc, &st, &smem) ? 1 : 0;
 }
 
+// gated: W is [2 N, K], N gate rows then N up rows, and out [M, N] = silu(x Wg^T) * (x Wu^T); no bias, no splits.
 // splits > 1 cuts K into that many equal parts (K %% (16 * splits) == 0): out is then float32
 // [splits][M][ldo-strided N] with split_stride elements between the parts, and the caller adds them.
 PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, void* out, int M, int N, int K,
                                long long ldx, long long ldw, long long ldo, int out_f32, int splits, long long split_stride,
-                               int* status, cudaStream_t stream) {
+                               int gated, int* status, cudaStream_t stream) {
+    PB_REQUIRE(!gated || (splits == 1 && bias == nullptr), "gemm_stream: the gated form takes no bias and no cut of K");
     PB_REQUIRE(splits >= 1 && splits <= 16 && (splits == 1 || K % (16 * splits) == 0), "gemm_stream: K=%d cannot be cut into %d parts of whole 16-element steps", K, splits);
     PB_REQUIRE(splits == 1 || (out_f32 && split_stride >= (long long)(M - 1) * ldo + N), "gemm_stream: partial sums are float32, %d apart at least", M * N);
     const int k_part = K / splits;
@@ -330,6 +360,7 @@ PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, 
     p.W = (const __nv_bfloat16*)W; p.X = (const __nv_bfloat16*)X; p.out = out; p.bias = bias;
     p.ldw = ldw; p.ldx = ldx; p.ldo = ldo; p.M = M; p.N = N; p.K = k_part; p.out_f32 = out_f32; p.status = status;
     p.split_stride = split_stride;
+    p.gated = gated ? 1 : 0;
     size_t smem;
     gs_plan(M, k_part, &p.ks, &p.n_chunks, &p.stages, &smem);
     int blocks = gs_sms() / splits;

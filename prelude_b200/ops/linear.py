@@ -41,25 +41,37 @@ def stream_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                out_dtype: torch.dtype = torch.bfloat16, splits: int = 1) -> torch.Tensor:
+                out_dtype: torch.dtype = torch.bfloat16, splits: int = 1, gated: bool = False) -> torch.Tensor:
     """The weight-streaming product for up to 16 rows of x; raises when the shape is not taken.
     With ``splits`` > 1, K is cut into that many parts and the result is the float32 partial
-    sums [splits, M, N], for a reader that adds them up (``PartialSums``)."""
+    sums [splits, M, N], for a reader that adds them up (``PartialSums``).  With ``gated``,
+    weight is [2 N, K] (N gate rows, then N up rows) and the result is silu(gate) * up, [M, N]."""
     M, Kdim = x.shape
-    N = weight.shape[0]
+    N = weight.shape[0] // 2 if gated else weight.shape[0]
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelLibraryError("gemm_stream: output must be bfloat16 or float32")
     if x.stride(1) != 1 or weight.stride(1) != 1:
         raise KernelLibraryError("gemm_stream: rows must be dense")
+    if gated and weight.shape[0] % 2:
+        raise KernelLibraryError("gemm_stream: a gated weight has as many up rows as gate rows")
     if splits > 1:
         out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
     else:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     check(_l.library().pb_gemm_stream_bf16(
         x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), M, N, Kdim,
-        x.stride(0), weight.stride(0), N, 1 if out.dtype == torch.float32 else 0, splits, M * N,
+        x.stride(0), weight.stride(0), N, 1 if out.dtype == torch.float32 else 0, splits, M * N, 1 if gated else 0,
         tc_status(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream), "gemm_stream")
     return out
+
+
+def gated_linear_silu(x: torch.Tensor, weight_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
+    """silu(x Wg^T) * (x Wu^T) for the merged [gate; up] weight in one kernel, where the streaming
+    kernel takes the shape (a decode step); None otherwise - the caller then multiplies and
+    activates in two steps."""
+    if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and stream_takes(x, weight_gate_up):
+        return gemm_stream(x, weight_gate_up, gated=True)
+    return None
 
 
 _tc_scratch: Dict[torch.device, torch.Tensor] = {}

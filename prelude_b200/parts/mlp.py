@@ -14,7 +14,7 @@ import torch
 
 from ..config.spec import GatedMlpSpec
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import gated_linear_silu, linear
 from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
 
@@ -49,5 +49,7 @@ class GatedMlp:
     def forward(self, x: torch.Tensor):
         """The feed-forward of x; what comes back goes to a fused residual add, which also takes
         the partial sums of a product whose K was cut into parts."""
-        gate_up = linear(x, self.w_gate_up)
-        return linear(_ACTIVATIONS[self.spec.activation](gate_up), self.w_down, partial_sums_ok=True)
+        act = gated_linear_silu(x, self.w_gate_up) if self.spec.activation == "silu" else None
+        if act is None:
+            act = _ACTIVATIONS[self.spec.activation](linear(x, self.w_gate_up))
+        return linear(act, self.w_down, partial_sums_ok=True)

@@ -534,6 +534,20 @@ def test_gemm_stream(M, N, K_):
     assert int(tc_status(x.device).item()) == 0
 
 
+@pytest.mark.parametrize("M,I,K_", [(8, 9728, 2560), (1, 200, 64), (16, 77, 96), (3, 8, 32), (5, 1000, 1504)])
+def test_gemm_stream_gated(M, I, K_):
+    # silu(x Wg^T) * (x Wu^T) from the merged weight, against the two-step computation in float64
+    from prelude_b200.ops.linear import gated_linear_silu, gemm_stream
+    x, w = rnd(M, K_, dtype=torch.bfloat16, seed=31), rnd(2 * I, K_, dtype=torch.bfloat16, seed=32, scale=0.05)
+    g, u = x.double() @ w[:I].double().T, x.double() @ w[I:].double().T
+    want = g / (1 + torch.exp(-g)) * u
+    got = gemm_stream(x, w, gated=True)
+    assert got.shape == (M, I) and got.dtype == torch.bfloat16
+    assert (got.double() - want).abs().max() <= tol(torch.bfloat16, float(want.abs().max()))
+    assert torch.equal(gated_linear_silu(x, w), got)
+    assert gated_linear_silu(rnd(40, K_, dtype=torch.bfloat16), w) is None      # too many rows: the caller takes two steps
+
+
 def test_gemm_stream_finds_the_one_weight_that_matters():
     # one large product at the far end of K and of N, everything else small: a lost chunk or row shows
     from prelude_b200.ops.linear import gemm_stream
