@@ -60,11 +60,19 @@ template <typename TX, typename TY, int ITERS>
 __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride, float* __restrict__ res,
                                         const float* __restrict__ w, TY* __restrict__ y, int width, float eps) {
     pb_grid_dep_launch();
-    pb_grid_dep_wait();
     __shared__ float red[32];
     size_t row = blockIdx.x;
     float4* r4 = reinterpret_cast<float4*>(res + row * width);
     const int n4 = width >> 2;
+    // the scale is written by no kernel: it is fetched while the kernel before this one is still running
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4 scale[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) scale[it] = w4[i];
+    }
+    pb_grid_dep_wait();
     float4 keep[ITERS];
     float ss = 0.f;
 #pragma unroll
@@ -93,12 +101,11 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
     }
     float total = block_sum(ss, red);
     float inv = 1.0f / sqrtf(total / (float)width + eps);
-    const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
         int i = threadIdx.x + it * blockDim.x;
         if (i < n4) {
-            float4 v = keep[it], g = w4[i];
+            float4 v = keep[it], g = scale[it];
             float o0 = v.x * inv * g.x, o1 = v.y * inv * g.y, o2 = v.z * inv * g.z, o3 = v.w * inv * g.w;
             TY* out = y + row * width + 4 * (size_t)i;
             if constexpr (sizeof(TY) == 2) {

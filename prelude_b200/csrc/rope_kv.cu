@@ -115,7 +115,6 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
     int n_tokens, int n_heads, int n_kv_heads, int write_kv, int swizzle, int* __restrict__ status) {
     pb_grid_dep_launch();
-    pb_grid_dep_wait();
     constexpr int D = LANES * 8;
     const int heads_per_token = n_heads + (write_kv ? 2 * n_kv_heads : 0);
     const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;     // (token, head) of this lane
@@ -124,6 +123,9 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     // lanes without a row keep going (the shuffles below are warp-wide) on row 0 and store nothing
     const int t = live ? (int)(group / heads_per_token) : 0;
     const int slot = live ? (int)(group % heads_per_token) : 0;
+    // Positions, block tables, norm scales and the rotation tables were written before this step's first kernel
+    // started: everything that depends on them alone is fetched before the wait for the kernel ahead (which
+    // writes q, k and v).
     const int pos = positions[t];
     const bool is_q = slot < n_heads, is_k = !is_q && slot < n_heads + n_kv_heads;
     const int h = is_q ? slot : (is_k ? slot - n_heads : slot - n_heads - n_kv_heads);
@@ -144,6 +146,31 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
             dst = (is_k ? k_pages : v_pages) + (((size_t)page * n_kv_heads + h) * page_size + in_page) * D + cc * 8;
         }
     }
+    const float* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+    if (weight != nullptr) {
+        w0 = *reinterpret_cast<const float4*>(weight + c * 8);
+        w1 = *reinterpret_cast<const float4*>(weight + c * 8 + 4);
+    }
+    // rotation: element j of the first half pairs with j + half; the partner chunk sits half / 8 lanes away
+    const int half = (cos_table != nullptr) ? rotary_dim / 2 : 0;
+    const int hc = half / 8;                                                                 // chunks per half (0: no rotation)
+    const bool first = c < hc, second = c >= hc && c < 2 * hc;
+    const bool rotates = (first || second) && (is_q || is_k);
+    float4 c0 = make_float4(1.f, 1.f, 1.f, 1.f), c1 = c0, s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+    if (rotates) {
+        if (pos < 0 || pos >= max_positions) {
+            if (live && c == 0 && status) atomicExch(status, 3);
+            store = false;
+        } else {
+            const int j0 = (first ? c : c - hc) * 8;
+            const float* cp = cos_table + (size_t)pos * half + j0;
+            const float* sp = sin_table + (size_t)pos * half + j0;
+            c0 = *reinterpret_cast<const float4*>(cp); c1 = *reinterpret_cast<const float4*>(cp + 4);
+            s0 = *reinterpret_cast<const float4*>(sp); s1 = *reinterpret_cast<const float4*>(sp + 4);
+        }
+    }
+    pb_grid_dep_wait();
     const uint4 raw = *reinterpret_cast<const uint4*>(src);
     if (!is_q && !is_k) {                                                                    // values: plain copy
         if (store) *reinterpret_cast<uint4*>(dst) = raw;
@@ -155,7 +182,6 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h2[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
     }
-    const float* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
@@ -163,34 +189,19 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);       // over the lanes of the row
     if (weight != nullptr) {
         const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-        const float4 w0 = *reinterpret_cast<const float4*>(weight + c * 8), w1 = *reinterpret_cast<const float4*>(weight + c * 8 + 4);
         x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
         x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
     }
-    // rotation: element j of the first half pairs with j + half; the partner chunk sits half / 8 lanes away
-    const int half = (cos_table != nullptr) ? rotary_dim / 2 : 0;
-    const int hc = half / 8;                                                                 // chunks per half (0: no rotation)
-    const bool first = c < hc, second = c >= hc && c < 2 * hc;
     const int partner = first ? c + hc : (second ? c - hc : c);
     const int src_lane = (threadIdx.x & 31) - c + partner;
     float y[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[i] = __shfl_sync(0xffffffffu, x[i], src_lane);
-    if ((first || second) && (is_q || is_k)) {
-        if (pos < 0 || pos >= max_positions) {
-            if (live && c == 0 && status) atomicExch(status, 3);
-            store = false;
-        } else {
-            const int j0 = (first ? c : c - hc) * 8;
-            const float* cp = cos_table + (size_t)pos * half + j0;
-            const float* sp = sin_table + (size_t)pos * half + j0;
-            const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
-            const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
-            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    if (rotates) {
+        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = first ? x[i] * cs[i] - y[i] * sn[i] : x[i] * cs[i] + y[i] * sn[i];
-        }
+        for (int i = 0; i < 8; ++i) x[i] = first ? x[i] * cs[i] - y[i] * sn[i] : x[i] * cs[i] + y[i] * sn[i];
     }
     if (store && (is_q || is_k)) {
         uint4 out;
