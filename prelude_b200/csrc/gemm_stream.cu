@@ -17,7 +17,8 @@
 //    a whole row where it fits.  Weights are written by no kernel, so the
 //    loaders fill the ring before they wait for the kernel before this one on
 //    the stream: the stream is already flowing when x becomes available.
-//  * x (a few KB per row) is copied whole into shared memory after that wait.
+//  * x (a few KB per row) is copied whole into shared memory by the compute warps
+//    the moment that kernel is done.
 //  * Eight compute warps share the 16-element steps of every pair of stages; W is
 //    the row operand of mma.m16n8k16 (16 features: ldmatrix takes its 16 row
 //    addresses from the two stages), x the column operand (8 batch rows per
@@ -129,36 +130,26 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
         // ---------------- loaders: warp j copies rows 2 j and 2 j + 1 of every stage (lanes 0 and 1) ----------------
         const int lw = warp - GS_WARPS;
         constexpr int PER = GS_ROWS / GS_LOADERS;
-        bool ok = true, x_sent = false;
+        bool ok = true;
         int stage = 0, phase = 0, i = 0;
-        auto fetch_x = [&]() {
-            // the ring is full (or all is issued): now wait for the kernel that produces x, and fetch x;
-            // warp j brings rows j, j + 4, ...
-            pb_grid_dep_wait();
-            const int mine = (p.M - lw + GS_LOADERS - 1) / GS_LOADERS;
-            if (lane == 0) mbar_arrive_expect_tx(&x_bar, (unsigned)max(mine, 0) * p.K * 2);
-            __syncwarp();
-            const int m = lw + lane * GS_LOADERS;
-            if (m < p.M) bulk_copy_g2s(sX + (size_t)m * x_stride, p.X + (size_t)m * p.ldx, (unsigned)p.K * 2, &x_bar);
-            x_sent = true;
-        };
 #pragma unroll 1
         for (int tile = 0; tile < n_tiles && ok; ++tile) {
             const int halves = (p.gated || r1 - (r0 + tile * span) > GS_ROWS) ? 2 : 1;
 #pragma unroll 1
             for (int kc = 0; kc < p.n_chunks && ok; ++kc) {
                 for (int h = 0; h < halves; ++h, ++i) {
-                    if (!x_sent && i >= p.stages) fetch_x();
-                    ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1);
-                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    if (i >= p.stages) {                       // the first ring-full finds every stage free
+                        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1);
+                        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    }
                     if (lw == 0 && lane == 0) *(volatile int*)&s_issued = i + 1;   // the stage's previous tenant has been consumed
                     const int feat0 = r0 + tile * span + (p.gated ? 0 : h * GS_ROWS);   // first feature of the stage
                     const int row0 = feat0 + (p.gated ? h * p.N : 0);                 // its row of W: up rows follow the gate rows
                     const int k0 = kc * p.ks, len = min(p.ks, p.K - k0);
                     const int n_rows = min(GS_ROWS, r1 - feat0);
                     const int mine = min(PER, max(0, n_rows - lw * PER));        // rows of this stage that this warp brings
+                    // the copies may land before the expected bytes are posted: the phase cannot end before this arrival
                     if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], (unsigned)mine * len * 2);
-                    __syncwarp();
                     const int rr = lw * PER + lane;
                     if (lane < mine)
                         bulk_copy_g2s(ring + (size_t)stage * stage_bytes + (size_t)rr * w_stride,
@@ -168,13 +159,20 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
             }
         }
         if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
-        if (!x_sent) fetch_x();
         return;
     }
 
     // ---------------- compute warps ----------------
     pb_grid_dep_wait();                                        // the output may still be in use by the kernel before
     const int g = lane >> 2, t4 = lane & 3;
+    if (warp < GS_LOADERS) {
+        // x is this kernel's only input that another kernel writes: the first four compute warps fetch it the
+        // moment that kernel is done (warp j brings rows j, j + 4, ...), whatever the loaders are busy with
+        const int mine = (p.M - warp + GS_LOADERS - 1) / GS_LOADERS;
+        if (lane == 0) mbar_arrive_expect_tx(&x_bar, (unsigned)max(mine, 0) * p.K * 2);
+        const int m = warp + lane * GS_LOADERS;
+        if (m < p.M) bulk_copy_g2s(sX + (size_t)m * x_stride, p.X + (size_t)m * p.ldx, (unsigned)p.K * 2, &x_bar);
+    }
     // A warp that gives up waiting says so in s_dead; the compute warps meet at their barrier all the same
     // and leave together, so none is left waiting for one that has gone.
     if (!__all_sync(0xffffffffu, mbar_wait_bounded(&x_bar, 0))) {
