@@ -28,7 +28,7 @@ from .graph import DecodeGraphs
 from .loading import load_model, parse_dtype
 from ..parts.model import DecoderModel
 from .runner import ModelRunner, StepEntry
-from .scheduler import CachePoolView, SamplingParams, Scheduler, SchedulerConfig
+from .scheduler import ScheduledItem, CachePoolView, SamplingParams, Scheduler, SchedulerConfig
 
 
 @dataclass
@@ -72,7 +72,7 @@ class Engine:
                  max_running_requests: int = 256, max_num_batched_tokens: int = 8192,
                  long_prefill_token_threshold: int = 0, max_total_tokens: int = 0, decode_reservation_cap: int = 0,
                  decode_priority_max_remaining_tokens: int = 4, cuda_graph: bool = True, cuda_graph_max_bs: int = 64,
-                 max_model_len: Optional[int] = None):
+                 max_model_len: Optional[int] = None, decode_burst: int = 8):
         """``model`` is a folder with config.json and safetensors files (or a
         DecoderModel that is already on the device).
 
@@ -117,6 +117,10 @@ class Engine:
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self.cuda_graph = cuda_graph
         self.graphs = DecodeGraphs(self.runner, cuda_graph_max_bs) if cuda_graph else None
+        # Runs of decode steps queued without the host in between (see _burst_length): up to this many
+        self.decode_burst = max(1, int(decode_burst))
+        self.burst_graphs = (DecodeGraphs(self.runner, cuda_graph_max_bs, self_feeding=True)
+                             if cuda_graph and self.decode_burst > 1 else None)
         self._stats = EngineStats(pages_total=int(num_pages))
         self._next_id = 0
 
@@ -146,7 +150,10 @@ class Engine:
         for bs in sizes:
             if bs in self.graphs.graphs and self.graphs.graphs[bs].graph is not None:
                 continue
-            self.generate([[0]] * bs, temperature=0.0, max_new_tokens=3, ignore_eos=True)
+            # two tokens: the second comes from a single captured step; five: from a queued run of steps
+            self.generate([[0]] * bs, temperature=0.0, max_new_tokens=2, ignore_eos=True)
+            if self.burst_graphs is not None:
+                self.generate([[0]] * bs, temperature=0.0, max_new_tokens=5, ignore_eos=True)
             if bs in self.graphs.graphs:
                 done.append(bs)
         return done
@@ -203,6 +210,13 @@ class Engine:
                 if sched.has_work():
                     raise RuntimeError("the scheduler has work but could schedule nothing")
                 break
+            burst = self._burst_length(sched, items)
+            if burst >= 2:
+                for j, tokens in enumerate(self._run_burst(items, burst)):
+                    for it, tok in zip(items, tokens):
+                        sched.on_step_done(it if j == 0 else ScheduledItem(it.seq, 1, it.start + j), tok, self.eos_token_ids)
+                self._collect(sched, done, first_token_at, t0)
+                continue
             tokens = self._run_step(items)
             now = time.perf_counter()
             for it, tok in zip(items, tokens):
@@ -220,6 +234,61 @@ class Engine:
                 seq.request_id, list(seq.output), seq.finish_reason or "abort", len(seq.prompt), len(seq.output),
                 ttft_ms=(first_token_at.get(seq.request_id, now) - t0) * 1e3, total_ms=(now - t0) * 1e3,
                 preemptions=seq.preempt_count)
+
+    def _burst_length(self, sched: Scheduler, items) -> int:
+        """How many decode steps may be queued on the device without the host looking at the
+        tokens in between.  A graph launch costs the host about as much as a tenth of a step
+        of a 4B model; with the sampled token fed to the next step on the device, the launches
+        of a run overlap the steps before them.  A run is taken when nothing could change the
+        batch before it ends: every running request is in the step and decoding, nobody is
+        waiting, sampling runs on the device (greedy or temperature), every request still has
+        that many tokens to go (one that stops early - end of sequence, a stop token - has
+        its later tokens dropped), and the pages for all of it are free."""
+        if self.burst_graphs is None or sched.waiting or len(items) != len(sched.running):
+            return 1
+        if not all(it.n_tokens == 1 and it.samples for it in items):
+            return 1
+        if any(sampling_mode(it.seq.params.temperature, it.seq.params.top_k, it.seq.params.top_p) not in ("greedy", "all")
+               for it in items):
+            return 1
+        k = min(self.decode_burst, min(it.seq.max_new_tokens - len(it.seq.output) for it in items))
+        if k < 2 or not self.burst_graphs.usable(len(items), max(it.start + k for it in items)):
+            return 1
+        demand: Dict[int, int] = {}
+        for it in items:
+            rid = it.seq.request_id
+            if not self.cache.has_request(rid):
+                return 1
+            for gid, n in self.cache.pages_needed(rid, it.start + k).items():
+                demand[gid] = demand.get(gid, 0) + n
+        if any(n > self.cache.groups[gid].allocator.num_free for gid, n in demand.items()):
+            return 1
+        return k
+
+    def _run_burst(self, items, k: int) -> List[List[int]]:
+        """``k`` decode steps of the same requests, queued at once; the tokens of every step."""
+        t0 = time.perf_counter()
+        entries = [StepEntry(it.seq.request_id, it.seq.tokens[it.start:it.start + 1], [0]) for it in items]
+        starts = self.runner.reserve(entries)
+        for it in items:
+            self.cache.grow(it.seq.request_id, it.start + k)
+        self.cache.flush_table_updates()
+        self.cache.zero_fresh_state()
+        g = self.burst_graphs.get(len(items))
+        g.load([e.tokens[0] for e in entries], starts, [self.cache.slot_of(e.request_id) for e in entries],
+               [it.seq.params.temperature for it in items], [it.seq.params.seed for it in items],
+               [len(it.seq.output) for it in items])
+        steps = g.replay_burst(k)
+        for e in entries:
+            self.cache.trim(e.request_id)
+        st = self._stats
+        st.graph_steps += k
+        st.steps += k
+        st.decode_steps += k
+        st.generated_tokens += k * len(items)
+        st.pages_in_use_peak = max(st.pages_in_use_peak, self.cache.used_pages())
+        st.step_ms_total += (time.perf_counter() - t0) * 1e3
+        return steps
 
     def _run_step(self, items) -> List[Optional[int]]:
         """Run one scheduled step; returns the sampled token per item (None

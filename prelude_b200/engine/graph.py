@@ -54,6 +54,7 @@ class DecodeGraph:
         self.host_samp = torch.zeros(3 * bs, dtype=torch.int64, pin_memory=True)   # temps bits | seeds | counters
         self.dev_samp = torch.zeros(3 * bs, dtype=torch.int64, device=dev)
         self.host_out = torch.zeros(bs + 1, dtype=torch.int32, pin_memory=True)
+        self.host_burst: Optional[torch.Tensor] = None      # [steps, bs] sampled tokens of a queued run of replays
         self.batch = StepBatch(
             n_tokens=bs, n_seqs=bs, token_ids=self.tokens, positions=self.positions, token_seq=self.slots,
             cu_q=self.ints[4 * bs:5 * bs + 1], q_start=self.positions, kv_len=self.positions,
@@ -79,14 +80,15 @@ class DecodeGraph:
     def capture(self) -> None:
         """Warm up once eagerly on the current buffer contents, then capture."""
         from ..ops import library
-        saved = self.ints.clone()
+        saved, saved_samp = self.ints.clone(), self.dev_samp.clone()
         stream = torch.cuda.Stream(device=self.runner.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             self._body()
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
-        self.ints.copy_(saved)          # a self-feeding warm-up has moved tokens and positions
+        self.ints.copy_(saved)          # a self-feeding warm-up has moved tokens, positions and counters
+        self.dev_samp.copy_(saved_samp)
         before = library.launch_count
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
@@ -94,6 +96,7 @@ class DecodeGraph:
         self.launches = library.launch_count - before
         self.graph = graph
         self.ints.copy_(saved)
+        self.dev_samp.copy_(saved_samp)
 
     def load(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
              temperatures: Sequence[float], seeds: Sequence[int], counters: Sequence[int]) -> None:
@@ -121,6 +124,22 @@ class DecodeGraph:
             self.capture()
         self.graph.replay()
 
+    def replay_burst(self, steps: int) -> List[List[int]]:
+        """Queue ``steps`` replays of a self-feeding graph - every step's input is the step before's
+        output, on the device - and return the sampled tokens of every step.  The host waits once."""
+        if not self.self_feeding:
+            raise RuntimeError("a run of replays needs a self-feeding graph")
+        if self.host_burst is None or self.host_burst.shape[0] < steps:
+            self.host_burst = torch.zeros((max(steps, 8), self.bs), dtype=torch.int32, pin_memory=True)
+        for j in range(steps):
+            self.replay()
+            self.host_burst[j].copy_(self.sampled, non_blocking=True)   # in stream order, before the next replay overwrites it
+        self.host_out[self.bs:].copy_(self.status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        if int(self.host_out[self.bs]) != 0:
+            raise RuntimeError(f"a kernel met a bad page id or position during the step (code {int(self.host_out[self.bs])})")
+        return self.host_burst[:steps].tolist()
+
     def fetch(self) -> List[int]:
         """Sampled tokens of the last replay (one device-to-host copy, then a wait)."""
         self.host_out[:self.bs].copy_(self.sampled, non_blocking=True)
@@ -133,10 +152,12 @@ class DecodeGraph:
 
 
 class DecodeGraphs:
-    """Captured steps by batch size, made when first needed."""
+    """Captured steps by batch size, made when first needed.  ``self_feeding`` graphs end
+    with the kernel that turns the sampled tokens into the next step's input, so several
+    replays can be queued without the host in between."""
 
-    def __init__(self, runner, max_batch_size: int):
-        self.runner, self.max_bs = runner, max_batch_size
+    def __init__(self, runner, max_batch_size: int, self_feeding: bool = False):
+        self.runner, self.max_bs, self.self_feeding = runner, max_batch_size, self_feeding
         self.graphs: Dict[int, DecodeGraph] = {}
 
     def usable(self, batch_size: int, longest: int) -> bool:
@@ -147,5 +168,5 @@ class DecodeGraphs:
     def get(self, batch_size: int) -> DecodeGraph:
         g = self.graphs.get(batch_size)
         if g is None:
-            g = self.graphs[batch_size] = DecodeGraph(self.runner, batch_size)
+            g = self.graphs[batch_size] = DecodeGraph(self.runner, batch_size, self_feeding=self.self_feeding)
         return g

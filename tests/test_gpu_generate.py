@@ -105,6 +105,32 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(folders):
     assert [r.token_ids for r in p1] == [r.token_ids for r in p2]
 
 
+def test_queued_runs_of_decode_steps_give_the_tokens_of_single_steps(folders):
+    """With decode_burst > 1 the engine queues several decode steps and reads their tokens at the end;
+    requests of different lengths, stops in the middle of a run and seeded sampling come out the same
+    as with one step at a time."""
+    prompts = _prompts("B", [2, 9, 31, 64])
+    single, burst = _engine(folders["B"], page_size=8, decode_burst=1), _engine(folders["B"], page_size=8, decode_burst=5)
+    for kw in (dict(temperature=0.0, max_new_tokens=13, ignore_eos=True),
+               dict(temperature=0.8, seed=5, max_new_tokens=11, ignore_eos=True),
+               dict(temperature=0.0, max_new_tokens=12)):                       # eos ids 7 and 9 may cut requests short
+        a, b = single.generate(prompts, **kw), burst.generate(prompts, **kw)
+        assert [r.token_ids for r in a] == [r.token_ids for r in b]
+        assert [r.finish_reason for r in a] == [r.finish_reason for r in b]
+    assert burst.stats().graph_steps > 0 and burst.cache.used_pages() == 0
+    # a stop token in the middle of a run: the tokens after it are dropped
+    free = single.generate(prompts[1], temperature=0.0, max_new_tokens=12, ignore_eos=True).token_ids
+    a = single.generate(prompts[1], temperature=0.0, max_new_tokens=12, ignore_eos=True, stop_token_ids=[free[3]])
+    b = burst.generate(prompts[1], temperature=0.0, max_new_tokens=12, ignore_eos=True, stop_token_ids=[free[3]])
+    assert a.token_ids == b.token_ids and b.finish_reason == "stop" and len(b.token_ids) <= 4
+    # different lengths to go: the run is as long as the shortest, the rest goes on afterwards
+    params = [dict(max_new_tokens=n) for n in (3, 9, 14, 6)]
+    from prelude_b200 import SamplingParams
+    sp = [SamplingParams(temperature=0.0, ignore_eos=True, **p) for p in params]
+    a, b = single.generate(prompts, sp), burst.generate(prompts, sp)
+    assert [r.token_ids for r in a] == [r.token_ids for r in b] and [len(r.token_ids) for r in b] == [3, 9, 14, 6]
+
+
 def test_when_pages_run_out_requests_are_preempted_and_still_get_the_same_tokens(folders):
     cfg = tiny.PARAMS["A"][0]
     w = tiny.read_weights(folders["A"])
