@@ -48,8 +48,7 @@
 //    step's status word and goes on to the end.
 #include "attention_common.cuh"
 
-#define DEC_THREADS 256
-#define DEC_LOADERS 128
+#define DEC_LOADERS 128         // threads of the lsu path's four loader warps
 #define DEC_MAX_PAGES 512       // page ids of one block's share kept in shared memory (else read from the table)
 
 struct DecodeParams {
@@ -64,12 +63,15 @@ struct DecodeParams {
 // A barrier wait can tell only the current phase from the one before it, so a consumer must not start
 // to wait for tile i before tile i - STAGES (the stage's previous tenant) has been consumed: it first
 // waits until the loaders have announced tile i (s_issued), which they do only after that.
-template <int DMAX, bool BULK> struct DecodeTiling {
+// PAIR: two blocks per multiprocessor with half the ring each, for steps with more (token, head) pairs than
+// multiprocessors - one block's start and end then overlap the other's stream.  (Bulk path, head sizes up to 128.)
+template <int DMAX, bool BULK, bool PAIR> struct DecodeTiling {
     static constexpr int STRIDE = BULK ? DMAX : DMAX + 8;    // lsu: padded rows; bulk: dense rows with permuted chunks
     static constexpr int STAGE_ELEMS = 2 * BNW * STRIDE;     // K rows then V rows
-    static constexpr int FIT = (200 * 1024) / (STAGE_ELEMS * 2);
+    static constexpr int FIT = ((PAIR ? 98 : 200) * 1024) / (STAGE_ELEMS * 2);
     static constexpr int STAGES = FIT > 8 ? 8 : FIT;
     static constexpr int NC = STAGES < 4 ? STAGES : 4;       // consumer warps
+    static constexpr int THREADS = PAIR ? 160 : 256;         // four consumer warps and one loader warp (two blocks share the registers), or four
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -80,10 +82,11 @@ __device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <int DMAX, bool BULK>
-__global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParams dp) {
+template <int DMAX, bool BULK, bool PAIR>
+__global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PAIR ? 2 : 1)) attn_decode_kernel(DecodeParams dp) {
     pb_grid_dep_launch();
-    using T = DecodeTiling<DMAX, BULK>;
+    using T = DecodeTiling<DMAX, BULK, PAIR>;
+    constexpr int DEC_THREADS = T::THREADS;
     const AttnParams& p = dp.a;
     constexpr int STRIDE = T::STRIDE;
     constexpr int KSTEPS = DMAX / 16;
@@ -370,19 +373,38 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < G * d; idx += DEC_THREADS) {
-            const int row = idx / d, col = idx - row * d;
-            const float* po = p.part_o + (th0 + row) * ns * d + col;
-            float acc = 0.f;
+        // two output elements per thread and pass, their loads (up to 8 splits each) issued together
+        for (int idx0 = threadIdx.x; idx0 < G * d; idx0 += 2 * DEC_THREADS) {
+            float acc[2] = {0.f, 0.f};
             for (int s0 = 0; s0 < ns; s0 += 8) {
-                float v[8];
+                float v[2][8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = (s0 + u < ns) ? __ldcg(po + (size_t)(s0 + u) * d) : 0.f;
+                for (int e = 0; e < 2; ++e) {
+                    const int idx = idx0 + e * DEC_THREADS;
+                    const int row = idx / d, col = idx - row * d;
+                    const float* po = p.part_o + (th0 + row) * ns * d + col;
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (s0 + u < ns) acc += sMs[row * 64 + s0 + u] * v[u];
+                    for (int u = 0; u < 8; ++u) v[e][u] = (idx < G * d && s0 + u < ns) ? __ldcg(po + (size_t)(s0 + u) * d) : 0.f;
+                }
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int idx = idx0 + e * DEC_THREADS;
+                    if (idx < G * d) {
+                        const int row = idx / d;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (s0 + u < ns) acc[e] += sMs[row * 64 + s0 + u] * v[e][u];
+                    }
+                }
             }
-            p.out[(th0 + row) * d + col] = __float2bfloat16_rn(acc * sInv[row]);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int idx = idx0 + e * DEC_THREADS;
+                if (idx < G * d) {
+                    const int row = idx / d, col = idx - row * d;
+                    p.out[(th0 + row) * d + col] = __float2bfloat16_rn(acc[e] * sInv[row]);
+                }
+            }
         }
         return;
     }
@@ -403,29 +425,42 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) attn_decode_kernel(DecodeParam
     }
 }
 
-template <int DMAX, bool BULK> static size_t decode_smem() {
-    using T = DecodeTiling<DMAX, BULK>;
+template <int DMAX, bool BULK, bool PAIR> static size_t decode_smem() {
+    using T = DecodeTiling<DMAX, BULK, PAIR>;
     size_t tiles = (size_t)T::STAGES * T::STAGE_ELEMS * 2 + (size_t)16 * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
     size_t merge = (size_t)(4 * 16 * DMAX + 128 + 2 * 16 * 64 + 16) * 4;   // the warps' partial results, then the splits' maxima and sums
     return tiles > merge ? tiles : merge;
 }
 
-template <int DMAX, bool BULK>
+template <int DMAX, bool BULK, bool PAIR>
 static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
+    using T = DecodeTiling<DMAX, BULK, PAIR>;
     static bool configured = false;
-    size_t smem = decode_smem<DMAX, BULK>();
+    size_t smem = decode_smem<DMAX, BULK, PAIR>();
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DMAX, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DMAX, BULK, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return pb_fail("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    pb_launch(attn_decode_kernel<DMAX, BULK>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(DEC_THREADS), smem, stream, dp);
+    pb_launch(attn_decode_kernel<DMAX, BULK, PAIR>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(T::THREADS), smem, stream, dp);
     return 0;
 }
 
-// Blocks of this kernel that one multiprocessor holds at a time (for choosing the number of splits).
+static int g_dec_sms = 0;
+static int dec_sms() {
+    if (g_dec_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_dec_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_dec_sms <= 0) g_dec_sms = 148;
+    }
+    return g_dec_sms;
+}
+
+// Blocks of this kernel that one multiprocessor holds at a time when every (token, head) pair can have a
+// multiprocessor of its own (for choosing the number of splits).
 PB_API int pb_attention_decode_blocks_per_sm(int head_dim) {
-    size_t smem = head_dim <= 64 ? decode_smem<64, false>() : head_dim <= 128 ? decode_smem<128, false>() : decode_smem<256, false>();
+    size_t smem = head_dim <= 64 ? decode_smem<64, false, false>() : head_dim <= 128 ? decode_smem<128, false, false>() : decode_smem<256, false, false>();
     int n = (int)((227 * 1024) / (smem + 1024));
     return n < 1 ? 1 : n;
 }
@@ -472,10 +507,13 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
     // of 8 tokens (the rows then sit at the row numbers their permutation was made for)
     const bool bulk = swizzle && page_size % 8 == 0 && (BNW % page_size == 0 || page_size % BNW == 0) &&
                       (head_dim == 64 || head_dim == 128 || head_dim == 256);    // the dense layout has no room for a narrower head
-    int e = bulk ? (head_dim <= 64 ? launch_decode<64, true>(dp, stream)
-                    : head_dim <= 128 ? launch_decode<128, true>(dp, stream) : launch_decode<256, true>(dp, stream))
-                 : (head_dim <= 64 ? launch_decode<64, false>(dp, stream)
-                    : head_dim <= 128 ? launch_decode<128, false>(dp, stream) : launch_decode<256, false>(dp, stream));
+    // more blocks than multiprocessors: two per multiprocessor with half the ring each
+    const bool pair = bulk && head_dim <= 128 && (long long)n_tokens * n_kv_heads * n_splits > dec_sms();
+    int e = pair ? (head_dim == 64 ? launch_decode<64, true, true>(dp, stream) : launch_decode<128, true, true>(dp, stream))
+          : bulk ? (head_dim == 64 ? launch_decode<64, true, false>(dp, stream)
+                    : head_dim == 128 ? launch_decode<128, true, false>(dp, stream) : launch_decode<256, true, false>(dp, stream))
+                 : (head_dim <= 64 ? launch_decode<64, false, false>(dp, stream)
+                    : head_dim <= 128 ? launch_decode<128, false, false>(dp, stream) : launch_decode<256, false, false>(dp, stream));
     if (e) return e;
     PB_CHECK_LAUNCH("attention_decode");
     return 0;
