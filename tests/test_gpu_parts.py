@@ -271,3 +271,161 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
         assert [g.members for g in runner.cache.groups] == [[0]] and list(runner.cache.state_tensors) == [1]
     finally:
         unregister_part("mixer", "toy_decay")
+
+
+# ---------------------------------------------------------------------------------------
+# a toy feed-forward with routing, and another position encoding, both defined here
+# ---------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    expert_size: int
+    n_experts: int
+    kind: str = "toy_routed"
+
+
+@dataclass(frozen=True)
+class LinearAngleSpec:
+    """Rotation angles that grow linearly in the pair index (not geometrically), over half of the head."""
+    head_dim: int
+    rotary_dim: int
+    slope: float
+    max_positions: int
+    kind: str = "toy_linear_angle"
+
+
+def _register_toy_ff_and_position():
+    from prelude_b200.ops.linear import linear
+    from prelude_b200.parts.registry import register_part
+    from prelude_b200.weights.loader import TensorReq
+
+    @register_part("feed_forward", "toy_routed")
+    class RoutedFeedForward:
+        """Every token goes to the one expert its router logit (32-bit) is largest for:
+        y = p_e * down_e(relu(up_e x)), p = softmax(router x)."""
+
+        def __init__(self, spec, prefix):
+            self.spec, self.prefix = spec, prefix
+
+        def tensors(self):
+            s, p = self.spec, self.prefix
+            out = {f"{p}.router.weight": TensorReq((s.n_experts, s.hidden_size))}
+            for e in range(s.n_experts):
+                out[f"{p}.experts.{e}.up.weight"] = TensorReq((s.expert_size, s.hidden_size))
+                out[f"{p}.experts.{e}.down.weight"] = TensorReq((s.hidden_size, s.expert_size))
+            return out
+
+        def load(self, get, ctx):
+            s, p = self.spec, self.prefix
+            self.router = get(f"{p}.router.weight").to(ctx.device, torch.float32)
+            self.up = [get(f"{p}.experts.{e}.up.weight").to(ctx.device, ctx.dtype).contiguous() for e in range(s.n_experts)]
+            self.down = [get(f"{p}.experts.{e}.down.weight").to(ctx.device, ctx.dtype).contiguous() for e in range(s.n_experts)]
+
+        def forward(self, x):
+            probs = torch.softmax(x.float() @ self.router.T, dim=-1)
+            choice = probs.argmax(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.spec.n_experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(linear(x[rows].contiguous(), self.up[e]))
+                    out[rows] = (linear(h, self.down[e]).float() * probs[rows, e:e + 1]).to(x.dtype)
+            return out
+
+    @register_part("position", "toy_linear_angle")
+    class LinearAngle:
+        def __init__(self, spec, prefix=""):
+            self.spec = spec
+            self.cos = self.sin = None
+
+        def tensors(self):
+            return {}
+
+        def load(self, get, ctx):
+            s = self.spec
+            ang = _linear_angles(s.rotary_dim, s.max_positions, s.slope)
+            self.cos, self.sin = ang.cos().contiguous().to(ctx.device), ang.sin().contiguous().to(ctx.device)
+
+        @property
+        def rotary_dim(self):
+            return self.spec.rotary_dim
+
+
+def _linear_angles(rotary_dim, n_positions, slope):
+    j = torch.arange(rotary_dim // 2, dtype=torch.float32)
+    return torch.arange(n_positions, dtype=torch.float32)[:, None] * (slope * (1.0 + j))[None, :]
+
+
+def _plain_routed_and_linear_angle(cfg, w, ids, n_experts, rotary_dim, slope):
+    """Layer 0: attention rotating the first ``rotary_dim`` elements of every head by linearly spaced angles,
+    dense feed-forward; layer 1: the same attention, routed feed-forward.  Whole sequence, no cache."""
+    wf = {k: v.float() for k, v in w.items()}
+    L, eps = len(ids), cfg["rms_norm_eps"]
+    nH, nKV, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    ang = _linear_angles(rotary_dim, L, slope)
+    cos, sin = ang.cos(), ang.sin()
+
+    def rotate(x):                                           # [L, heads, D]: the first rotary_dim elements, half-split pairs
+        return torch.cat([plain.apply_rope(x[..., :rotary_dim], cos, sin), x[..., rotary_dim:]], dim=-1)
+
+    res = plain.embedding(torch.tensor(ids), wf["model.embed_tokens.weight"])
+    for i in range(2):
+        p = f"model.layers.{i}"
+        x = plain.rms_norm(res, wf[f"{p}.input_layernorm.weight"], eps)
+        q = plain.rms_norm((x @ wf[f"{p}.self_attn.q_proj.weight"].T).reshape(L, nH, D), wf[f"{p}.self_attn.q_norm.weight"], eps)
+        k = plain.rms_norm((x @ wf[f"{p}.self_attn.k_proj.weight"].T).reshape(L, nKV, D), wf[f"{p}.self_attn.k_norm.weight"], eps)
+        v = (x @ wf[f"{p}.self_attn.v_proj.weight"].T).reshape(L, nKV, D)
+        o = plain.causal_attention(rotate(q), rotate(k), v, 1.0 / math.sqrt(D))
+        res = res + o.reshape(L, nH * D) @ wf[f"{p}.self_attn.o_proj.weight"].T
+        x = plain.rms_norm(res, wf[f"{p}.post_attention_layernorm.weight"], eps)
+        if i == 0:
+            res = res + plain.swiglu_mlp(x, wf, f"{p}.mlp")
+        else:
+            probs = torch.softmax(x @ wf[f"{p}.mlp.router.weight"].T, dim=-1)
+            choice = probs.argmax(dim=-1)
+            y = torch.zeros_like(x)
+            for t in range(L):
+                e = int(choice[t])
+                h = torch.relu(x[t] @ wf[f"{p}.mlp.experts.{e}.up.weight"].T)
+                y[t] = probs[t, e] * (h @ wf[f"{p}.mlp.experts.{e}.down.weight"].T)
+            res = res + y
+    return plain.rms_norm(res, wf["model.norm.weight"], eps) @ wf["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_toy_routed_feed_forward_and_another_position_encoding(dtype):
+    """Two more parts from outside the package: a feed-forward that routes every token to one of three experts,
+    and a position encoding with its own angles over half of the head.  They are registered through the public
+    hook, chosen by the specs of single layers, and the model steps through every way of cutting."""
+    from prelude_b200.config import load_model_config
+    from prelude_b200.parts.registry import unregister_part
+    from prelude_b200.weights.random_init import random_tensors
+    _register_toy_ff_and_position()
+    try:
+        cfg, init, page = tiny.PARAMS["A"]
+        H, D, E, I = cfg["hidden_size"], cfg["head_dim"], 3, 40
+        spec = load_model_config(cfg).to_model_spec()
+        pos = LinearAngleSpec(D, D // 2, 0.07, cfg["max_position_embeddings"])
+        b0, b1 = spec.blocks
+        b0 = replace(b0, mixer=replace(b0.mixer, position=pos))
+        b1 = replace(b1, mixer=replace(b1.mixer, position=pos), feed_forward=RoutedSpec(H, I, E))
+        spec = replace(spec, blocks=(b0, b1))
+        g = torch.Generator().manual_seed(5)
+        w = {k: v for k, v in random_tensors(cfg, **init).items() if not k.startswith("model.layers.1.mlp.")}
+        w["model.layers.1.mlp.router.weight"] = torch.randn(E, H, generator=g)
+        for e in range(E):
+            w[f"model.layers.1.mlp.experts.{e}.up.weight"] = torch.randn(I, H, generator=g) * 0.1
+            w[f"model.layers.1.mlp.experts.{e}.down.weight"] = torch.randn(H, I, generator=g) * 0.1
+        w = {k: v.to(dtype) for k, v in w.items()}
+        reqs = {"x": tiny.random_ids(29, cfg["vocab_size"], 21), "y": tiny.random_ids(18, cfg["vocab_size"], 22)}
+        ref = {rid: _plain_routed_and_linear_angle(cfg, w, toks, E, D // 2, 0.07) for rid, toks in reqs.items()}
+        # the other position encoding matters: the model's own rotary tables give other logits
+        assert (ref["x"][-1] - plain.forward_logits(cfg, {k: v.float() for k, v in random_tensors(cfg, **init).items()}, reqs["x"])[-1]).abs().max() > 1e-3
+        for got in _run_model(spec, w, dtype, reqs, page):
+            assert len(got) == 47
+            for (rid, p), row in got.items():
+                want = ref[rid][p]
+                assert (row - want).abs().max() <= (2e-4 if dtype == torch.float32 else 4e-2 * float(want.abs().max()))
+    finally:
+        unregister_part("feed_forward", "toy_routed")
+        unregister_part("position", "toy_linear_angle")
