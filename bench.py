@@ -36,6 +36,13 @@ QWEN3_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_si
                 intermediate_size=9728, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
                 head_dim=128, max_position_embeddings=40960, rope_theta=1000000.0, rms_norm_eps=1e-6,
                 tie_word_embeddings=True, attention_bias=False, use_sliding_window=False, hidden_act="silu")
+# the layer sizes of the other two Qwen3 dense models, for --model-size (the default run is the 4B model)
+OTHER_SIZES = {
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, tie_word_embeddings=False),
+    "32b": dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                num_key_value_heads=8, head_dim=128, tie_word_embeddings=False),
+}
 CONTEXT_LEN, PREFIX_LEN, PAGE_SIZE, PREFILL_TOKENS = 4096, 2048, 16, 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
@@ -98,6 +105,9 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows)}
 
 
+MODEL = QWEN3_4B            # what --model-size chose
+
+
 def build_engine(layers, max_running, num_pages):
     import torch
     from prelude_b200 import Engine
@@ -105,7 +115,7 @@ def build_engine(layers, max_running, num_pages):
     from prelude_b200.engine.loading import build_model
     from prelude_b200.weights.loader import WeightStore
     from prelude_b200.weights.random_init import random_tensors
-    cfg = dict(QWEN3_4B, num_hidden_layers=layers)
+    cfg = dict(MODEL, num_hidden_layers=layers)
     tensors = random_tensors(cfg, seed=0, std=0.02, norm_jitter=0.05, dtype=torch.bfloat16, device="cuda:0")
     model = build_model(load_model_config(cfg).to_model_spec(), WeightStore.from_tensors(tensors), "bf16", "cuda:0")
     del tensors
@@ -228,12 +238,16 @@ def time_e2e(engine, cfg, batch, steps):
 
 
 def main():
+    global MODEL, PREFIX_LEN, CONTEXT_LEN
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--model-size", default="4b", choices=["4b", "8b", "32b"],
+                    help="layer sizes of another Qwen3 dense model (the headline run is 4b)")
+    ap.add_argument("--prefix-len", type=int, default=PREFIX_LEN, help="tokens every request holds before the timed decode steps")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     args = ap.parse_args()
@@ -246,6 +260,11 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus N with N > 1 is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.model_size != "4b":
+        MODEL = dict(QWEN3_4B, **OTHER_SIZES[args.model_size])
+    PREFIX_LEN = args.prefix_len
+    CONTEXT_LEN = max(CONTEXT_LEN, PREFIX_LEN + args.steps + args.warmup + 64)
+    args.layers = args.layers or MODEL["num_hidden_layers"]
     import torch
     pk = peaks()
     # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages
@@ -279,14 +298,15 @@ def main():
     achieved = step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
     pf = prefill_flops(cfg, PREFILL_TOKENS)
     line = {
-        "metric": "decode tok/s (Qwen3-4B sizes, random weights, bf16, batch 8, 2,048-token prefixes)",
+        "metric": f"decode tok/s (Qwen3-{args.model_size.upper()} sizes, random weights, bf16, batch {args.batch}, "
+                  f"{PREFIX_LEN:,}-token prefixes)",
         "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(dec["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "qwen3-4b-sizes", "layers": args.layers, "layers_full": QWEN3_4B["num_hidden_layers"],
+        "config": {"model": f"qwen3-{args.model_size}-sizes", "layers": args.layers, "layers_full": MODEL["num_hidden_layers"],
                    "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
                    "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
-                   "head_dim": cfg["head_dim"], "vocab_size": cfg["vocab_size"], "tie_word_embeddings": True,
+                   "head_dim": cfg["head_dim"], "vocab_size": cfg["vocab_size"], "tie_word_embeddings": cfg["tie_word_embeddings"],
                    "global_batch": args.batch, "seq_len": PREFIX_LEN, "context_len": CONTEXT_LEN,
                    "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single",
                    "l2": "inputs_exceed_l2", "peaks": pk["source"]},

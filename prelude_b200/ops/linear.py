@@ -33,11 +33,14 @@ TC_POLICY = os.environ.get("PRELUDE_TC_GEMM", "auto")
 _retired: List[torch.Tensor] = []          # outgrown buffers that captured graphs may still use
 
 
-def stream_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def stream_takes(x: torch.Tensor, weight: torch.Tensor, splits: int = 1) -> bool:
+    """Whether the streaming kernel takes x [M, K] against weight [N, K], K cut into ``splits`` parts."""
     M, Kdim = x.shape
+    if splits > 1 and Kdim % (16 * splits):
+        return False
     return (0 < M <= min(STREAM_MAX_ROWS, 16) and x.stride(1) == 1 and weight.stride(1) == 1
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
-            and bool(_l.library().pb_gemm_stream_supported(M, weight.shape[0], Kdim, weight.stride(0), x.stride(0))))
+            and bool(_l.library().pb_gemm_stream_supported(M, weight.shape[0], Kdim // splits, weight.stride(0), x.stride(0))))
 
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -149,10 +152,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if x.dtype == torch.bfloat16:
         if x.shape[0] == 0:
             return torch.empty((0, weight.shape[0]), dtype=out_dtype, device=x.device)
+        splits = stream_splits(x.shape[0], weight.shape[0], x.shape[1]) if partial_sums_ok else 1
+        if splits > 1 and stream_takes(x, weight, splits):      # a row of x too long for shared memory may still fit in parts
+            return K.PartialSums(gemm_stream(x, weight, bias, out_dtype, splits=splits))
         if stream_takes(x, weight):
-            splits = stream_splits(x.shape[0], weight.shape[0], x.shape[1]) if partial_sums_ok else 1
-            if splits > 1:
-                return K.PartialSums(gemm_stream(x, weight, bias, out_dtype, splits=splits))
             return gemm_stream(x, weight, bias, out_dtype)
         if _tc_wanted(x, weight, out_dtype) and tc_takes(x, weight):
             return gemm_tc(x, weight, bias, out_dtype)
