@@ -88,9 +88,16 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
                     float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
                     v.x += a.x; v.y += a.y; v.z += b.x; v.w += b.y;
                 } else {
-                    for (int s = 0; s < n_parts; ++s) {                              // the parts in ascending order
-                        float4 a = *reinterpret_cast<const float4*>(xr + s * part_stride);
-                        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    // the parts in ascending order, four loads in flight at a time
+                    for (int s0 = 0; s0 < n_parts; s0 += 4) {
+                        float4 a[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            a[u] = (s0 + u < n_parts) ? *reinterpret_cast<const float4*>(xr + (size_t)(s0 + u) * part_stride)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (s0 + u < n_parts) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
                     }
                 }
                 r4[i] = v;
