@@ -37,7 +37,8 @@ def build_parser() -> argparse.ArgumentParser:
                     help="Local path to model directory (config.json + safetensors)")
     ap.add_argument("--dtype", default="bf16", choices=["f32", "bf16", "float32", "bfloat16"],
                     help="Override dtype: f32 or bf16 (default bf16)")
-    ap.add_argument("--device", default="auto", help="Device: auto, cuda, cuda:N (there is no cpu path)")
+    ap.add_argument("--device", default=os.environ.get("PRELUDE_DEVICE", "auto"),
+                    help="Device: auto, cuda, cuda:N (there is no cpu path; env PRELUDE_DEVICE)")
     ap.add_argument("--max-running-requests", type=int, default=256, help="Max concurrent running requests in scheduler")
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192,
                     help="Per-step total token budget (prefill + decode combined)")
@@ -54,6 +55,12 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9,
                     help="Fraction of GPU memory for weights and KV cache (0.0-1.0). "
                          "Ignored when --num-pages or PRELUDE_PAGED_ATTN_BLOCKS is set.")
+    ap.add_argument("--chunked-prefill", dest="chunked_prefill", action="store_true", default=True,
+                    help="Cut prompts into portions under the per-step token budget, beside decode tokens (default)")
+    ap.add_argument("--no-chunked-prefill", dest="chunked_prefill", action="store_false",
+                    help="Whole prompts only: the per-step budget is raised to the longest request the model allows")
+    ap.add_argument("--decode-burst", type=int, default=8,
+                    help="Decode steps queued on the device at a time when nothing can change the batch (1 = off)")
     ap.add_argument("--cuda-graph", dest="cuda_graph", action="store_true", default=True,
                     help="Enable CUDA graph capture for decode steps")
     ap.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false",
@@ -102,10 +109,18 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     from .engine import Engine
     from .scheduler import SamplingParams
     try:
+        budget = args.max_num_batched_tokens
+        if not args.chunked_prefill:
+            # a prompt is never cut: the budget must hold the longest request (the reference instead runs
+            # prompt-only and decode-only steps in this mode, crates/prelude-core/src/scheduler/admission.rs:211-254)
+            from ..config import load_model_config
+            with open(os.path.join(args.model, "config.json"), "r", encoding="utf-8") as f:
+                limit = load_model_config(json.load(f)).to_model_spec().max_positions
+            budget = max(budget, args.max_model_len or limit)
         engine = Engine(args.model, dtype=args.dtype, device=device, page_size=args.page_size,
                         num_pages=args.num_pages or None, gpu_memory_utilization=args.gpu_memory_utilization,
                         max_running_requests=args.max_running_requests,
-                        max_num_batched_tokens=args.max_num_batched_tokens,
+                        max_num_batched_tokens=budget, decode_burst=args.decode_burst,
                         long_prefill_token_threshold=args.long_prefill_token_threshold,
                         max_total_tokens=args.max_total_tokens, decode_reservation_cap=args.decode_reservation_cap,
                         decode_priority_max_remaining_tokens=args.decode_priority_max_remaining_tokens,

@@ -168,6 +168,15 @@ def test_command_line(folders):
     cfg, w = tiny.PARAMS["A"][0], tiny.read_weights(folders["A"])
     assert [r["token_ids"] for r in lines] == [greedy_generate(cfg, w, p, 5) for p in ([5, 17, 3], [9, 8, 7, 6])]
     assert lines[0]["finish_reason"] == "length" and lines[0]["usage"] == {"prompt_tokens": 3, "completion_tokens": 5}
+    # whole prompts only, one decode step at a time, device from the environment: the same tokens
+    env = dict(os.environ, PRELUDE_DEVICE="cuda:0")
+    out2 = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "prelude"), "--model-path", folders["A"], "--dtype", "f32",
+                           "--prompt-ids", "5,17,3", "--prompt-ids", "9 8 7 6", "--max-tokens", "5", "--temperature", "0",
+                           "--num-pages", "16", "--page-size", "4", "--ignore-eos", "--no-chunked-prefill",
+                           "--max-num-batched-tokens", "2", "--decode-burst", "1"],
+                          capture_output=True, text=True, timeout=600, env=env)
+    assert out2.returncode == 0, out2.stderr
+    assert [json.loads(line)["token_ids"] for line in out2.stdout.strip().splitlines()] == [r["token_ids"] for r in lines]
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "prelude"), "--model", folders["A"], "--device", "cpu",
                           "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
     assert bad.returncode != 0 and "no cpu path" in bad.stderr
