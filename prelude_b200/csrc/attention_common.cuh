@@ -1,5 +1,6 @@
-// Helpers shared by the tensor-core attention kernels: asynchronous 16-byte copies,
-// ldmatrix, the bfloat16 mma, the parameter block and the page-gathering tile load.
+// Helpers shared by the tensor-core attention kernels (and the weight-streaming product): asynchronous
+// copies and their barriers, the bfloat16 mma, the parameter block, and the computation of one
+// 64-key attention tile.
 #pragma once
 #include "common.cuh"
 
@@ -51,22 +52,7 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem, const void* gmem, unsi
 // orders earlier ordinary shared-memory accesses of this thread before later asynchronous copies
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-    unsigned s = (unsigned)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-    unsigned s = (unsigned)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// the same product without `volatile`: the compiler may move it among the loads around it
+// m16n8k16 bfloat16 product with float32 accumulation; not `volatile`: the compiler may move it among the loads around it
 __device__ __forceinline__ void mma_bf16_free(float* c, const unsigned* a, unsigned b0, unsigned b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -100,36 +86,6 @@ struct AttnParams {
     float scale_log2;              // scale * log2(e)
     int* status;
 };
-
-// One tile of BN keys and values of one key/value head into shared memory;
-// rows outside [kv_begin, kv_end) (and rows whose page id is bad) are zero-filled.
-// Pages below kv_begin may have been given back already and are never looked up.
-template <int DMAX>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const AttnParams& p,
-                                             const int32_t* table, int kvh, int key0, int kv_begin, int kv_end) {
-    constexpr int STRIDE = DMAX + 8;
-    const int chunks = p.head_dim >> 3;                    // 16-byte chunks in a row
-    const int total = BN * chunks;
-    for (int c = threadIdx.x; c < total; c += ATT_THREADS) {
-        const int row = c / chunks, ch = c - row * chunks;
-        const int j = key0 + row;
-        bool ok = j >= kv_begin && j < kv_end;
-        size_t src = 0;
-        if (ok) {
-            const int page = table[j / p.page_size];
-            if (page < 0 || page >= p.num_pages) {
-                ok = false;
-                if (p.status) atomicExch(p.status, 6);
-            } else {
-                const int in_page = j % p.page_size;
-                src = (((size_t)page * p.n_kv_heads + kvh) * p.page_size + in_page) * p.head_dim + (p.swizzle ? ((ch ^ (in_page & 7)) * 8) : ch * 8);
-            }
-        }
-        cp_async16(sK + row * STRIDE + ch * 8, p.k_pages + src, ok);
-        cp_async16(sV + row * STRIDE + ch * 8, p.v_pages + src, ok);
-    }
-}
-
 
 // ---------------------------------------------------------------------------------------
 // the tile computation shared by the prefill and the decode kernel
@@ -349,4 +305,3 @@ static inline int attn_check_common(const char* name, const AttnParams& p) {
     return 0;
 }
 
-// Prompt portions (and any mix of portions and single tokens).  Tiles are listed by the host:

@@ -89,7 +89,6 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
     constexpr int DEC_THREADS = T::THREADS;
     const AttnParams& p = dp.a;
     constexpr int STRIDE = T::STRIDE;
-    constexpr int KSTEPS = DMAX / 16;
     constexpr int S = T::STAGES, NC = T::NC;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -153,11 +152,7 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
 
         const int n_tiles = (kt1 - kt0 + 1) * (BN / BNW);   // consumer tiles of BNW keys; tile i belongs to warp i % NC
         const int key_base = kt0 * BN;
-        // row r, 16-byte chunk c of a key or value tile (dense permuted rows, or padded rows)
-        const int row_elems = BULK ? d : STRIDE;
-        auto tile_at = [&](const __nv_bfloat16* base, int r, int c) {
-            return base + r * row_elems + ((BULK ? (c ^ (r & 7)) : c) << 3);
-        };
+        const int row_elems = BULK ? d : STRIDE;            // elements between rows of a key or value tile
         if (BULK && warp >= 4) {
             // ---------------- bulk loader: lane u of warp 4 fetches the u-th run of keys and of values ----------------
             if (warp == 4) {
