@@ -35,95 +35,14 @@
 // segment's stores overlap the next segment's products.  Every wait on a barrier
 // is bounded in time; a block that gives up raises the status word, frees its
 // tensor memory and returns.  No load uses cluster multicast.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
-#include <cuda.h>
 #include <stdlib.h>
 
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
-
-// ---------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem(bar)) : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_try(uint64_t* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// about a second at most; false on giving up
-__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, unsigned parity) {
-    if (tc_mbar_try(bar, parity)) return true;
-    const long long start = clock64();
-    while (clock64() - start < (1ll << 31)) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if (tc_mbar_try(bar, parity)) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tc_tma_load_2d(void* smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(tc_smem(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(tc_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_tmem_alloc(uint32_t* holder, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(holder)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tc_tmem_dealloc(uint32_t taddr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, unsigned accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// the barrier gets one arrival when all MMAs issued so far by this thread have finished
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem(bar)) : "memory");
-}
-// 16 consecutive float32 columns of this thread's lane
-__device__ __forceinline__ void tc_tmem_ld16(uint32_t taddr, float* v) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tc_bar_epilogue() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle
-// (what TMA writes for a {64 x rows} bfloat16 box): 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t tc_smem_desc(const void* tile) {
-    uint64_t d = 0;
-    d |= (uint64_t)((tc_smem(tile) & 0x3FFFF) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                                    // leading dimension byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                          // stride between 8-row groups
-    d |= (uint64_t)1 << 46;                                    // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                                    // 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = bn.
-__device__ __forceinline__ uint32_t tc_instr_desc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
 
 struct TcParams {
     void* out;                  // [rows_a, rows_b] bfloat16 or float32
@@ -381,22 +300,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn g_encode = nullptr;
-
-static int get_encode() {
-    if (g_encode) return 0;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
-        return pb_fail("gemm_tc: the driver does not offer cuTensorMapEncodeTiled (%s)", cudaGetErrorString(e));
-    g_encode = (EncodeTiledFn)fn;
-    return 0;
-}
-
 // a [rows, K] bfloat16 matrix with row stride ld (elements), boxes of {64 k, box_rows}
 static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, int box_rows) {
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};

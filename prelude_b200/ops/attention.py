@@ -8,6 +8,7 @@ rounding, never what is computed.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import numpy as np
@@ -16,6 +17,11 @@ import torch
 from . import kernels as K
 from . import library as _l
 from .library import check
+
+# Which kernel prompt portions run on: "auto" takes the tcgen05 kernel where it takes the shape and the step
+# has at least TC_MIN_TOKENS tokens, "tc" takes it wherever it takes the shape, "mma" never.
+PREFILL_KERNEL = os.environ.get("PRELUDE_PREFILL_ATTN", "auto")
+TC_MIN_TOKENS = int(os.environ.get("PRELUDE_PREFILL_TC_MIN_TOKENS", "1"))
 
 SM_COUNT = 148          # refreshed from the device at first use
 _sm_count_known = False
@@ -50,12 +56,11 @@ def decode_splits(n_tokens: int, n_kv_heads: int, head_dim: int, max_context: in
     return max(1, min(resident // blocks, tiles, 64))
 
 
-def _prefill_plan(batch, group: int):
-    """Tiles of 64 // group tokens per request, as device arrays (made once per step and group size)."""
-    key = ("attn_tiles", group)
+def _prefill_plan(batch, tpt: int):
+    """Tiles of ``tpt`` tokens per request, as device arrays (made once per step and tile size)."""
+    key = ("attn_tiles", tpt)
     plan = batch.extras.get(key)
     if plan is None:
-        tpt = 64 // group
         seqs, toks = [], []
         for r, n in enumerate(batch.q_lens.tolist()):
             starts = np.arange(0, n, tpt, dtype=np.int32)
@@ -108,7 +113,17 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
             None if counters is None else counters.data_ptr(), batch.status.data_ptr(), stream),
             "attention_decode")
         return out
-    tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, nH // nKV)
+    swizzled = 1 if K.kv_swizzled(q.dtype, D) else 0
+    if PREFILL_KERNEL != "mma" and lib.pb_attention_prefill_tc_supported(nH, nKV, D, page_size, swizzled) \
+            and (PREFILL_KERNEL == "tc" or T >= TC_MIN_TOKENS):
+        tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, lib.pb_attention_prefill_tc_tile_tokens(nH, nKV))
+        check(lib.pb_attention_prefill_tc_bf16(
+            q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
+            batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+            tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
+            swizzled, batch.status.data_ptr(), stream), "attention_prefill_tc")
+        return out
+    tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, 64 // (nH // nKV))
     check(lib.pb_attention_prefill_bf16(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
         batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),

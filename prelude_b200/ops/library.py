@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 
 class KernelLibraryError(RuntimeError):
@@ -40,6 +40,9 @@ _SIGNATURES = {
     "pb_softmax_temperature": ([P, L, I, I, P, P, P], I),
     "pb_philox_uniform": ([c_uint64, c_uint64], F),
     "pb_attention_prefill_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
+    "pb_attention_prefill_tc_supported": ([I, I, I, I, I], I),
+    "pb_attention_prefill_tc_tile_tokens": ([I, I], I),
+    "pb_attention_prefill_tc_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
     "pb_attention_decode_scratch_floats": ([I, I, I, I], L),
     "pb_attention_decode_blocks_per_sm": ([I], I),
     "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P], I),
