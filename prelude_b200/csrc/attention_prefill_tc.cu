@@ -166,11 +166,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
     } else if (warp == 9) {
         // ---------------- products: reads shared and tensor memory only ----------------
-        if (lane == 0) {
-            const uint32_t idesc_s = tc_instr_desc(PT_KEYS), idesc_o = tc_instr_desc(D, true);
-            bool ok = true;
-            // S_m = Q_m K^T for the key tile in `stage`
-            auto issue_s = [&](int m, int stage) {
+        // The whole warp walks the loop and waits; one elected lane issues.  (Issued from a branch on the lane
+        // number instead, every tcgen05.mma cost the thread about 100 cycles, more than the product itself takes;
+        // under elect.sync the descriptors stay in uniform registers and a 128 x 128 x 16 product issues every 64.)
+        const uint32_t idesc_s = tc_instr_desc(PT_KEYS), idesc_o = tc_instr_desc(D, true);
+        bool ok = true;
+        auto wait_all = [&](uint64_t* bar, unsigned parity) {
+            ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(bar, parity));
+            return ok;
+        };
+        // S_m = Q_m K^T for the key tile in `stage`; release_k: the key stage is free once these have finished
+        auto issue_s = [&](int m, int stage, bool release_k) {
+            tc_fence_after();
+            if (tc_elect_one()) {
                 const uint64_t dq = tc_smem_desc(sQ + m * T::TILE_BYTES), dk = tc_smem_desc(sKV + stage * 2 * T::TILE_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
@@ -178,49 +186,47 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tc_mma(tmem_base + m * PT_S_COLS, dq + off, dk + off, idesc_s, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(&s_full[m]);
-            };
-            // O_m (+)= P_m V for the value tile in `stage`
-            auto issue_o = [&](int m, int stage, bool first) {
+                if (release_k) tc_commit(&k_empty[stage]);
+            }
+            __syncwarp();
+        };
+        // O_m (+)= P_m V for the value tile in `stage`
+        auto issue_o = [&](int m, int stage, bool first, bool last, bool release_v) {
+            tc_fence_after();
+            if (tc_elect_one()) {
                 const uint64_t dv = tc_smem_desc_mn(sKV + stage * 2 * T::TILE_BYTES + T::TILE_BYTES, PT_SLAB);
 #pragma unroll
                 for (int ks = 0; ks < PT_KEYS / 16; ++ks)
                     tc_mma_ts(tmem_base + T::O_COL + m * D, tmem_base + m * PT_S_COLS + ks * 8, dv + ((ks * 16 * 128) >> 4), idesc_o,
                               (!first || ks > 0) ? 1u : 0u);
-            };
-            const auto first_active = [&](int j) { return j < n_m[0] ? 0 : 1; };
-            const auto last_active = [&](int j) { return j < n_m[1] ? 1 : 0; };
-            ok = mbar_wait_bounded(&q_full, 0) && mbar_wait_bounded(&k_full[0], 0);
-            if (ok) {
-                tc_fence_after();
-                for (int m = 0; m < 2; ++m)
-                    if (n_m[m] > 0) issue_s(m, 0);
-                tc_commit(&k_empty[0]);
+                if (last) tc_commit(&o_full[m]);
+                if (release_v) tc_commit(&v_empty[stage]);
             }
-            int stage = 0, phase = 0;
-#pragma unroll 1
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int nstage = stage + 1 == S ? 0 : stage + 1, nphase = stage + 1 == S ? phase ^ 1 : phase;
-                for (int m = 0; m < 2 && ok; ++m) {
-                    if (j >= n_m[m]) continue;
-                    ok = mbar_wait_bounded(&p_full[m], j & 1);
-                    if (ok && m == first_active(j)) ok = mbar_wait_bounded(&v_full[stage], phase);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_o(m, stage, j == 0);
-                    if (j == n_m[m] - 1) tc_commit(&o_full[m]);
-                    if (m == last_active(j)) tc_commit(&v_empty[stage]);
-                    if (j + 1 < n_m[m]) {
-                        if (m == first_active(j + 1)) ok = mbar_wait_bounded(&k_full[nstage], nphase);
-                        if (!ok) break;
-                        tc_fence_after();
-                        issue_s(m, nstage);
-                        if (m == last_active(j + 1)) tc_commit(&k_empty[nstage]);
-                    }
-                }
-                stage = nstage; phase = nphase;
-            }
-            if (!ok && p.status) atomicExch(p.status, 9);
+            __syncwarp();
+        };
+        const auto first_active = [&](int j) { return j < n_m[0] ? 0 : 1; };
+        const auto last_active = [&](int j) { return j < n_m[1] ? 1 : 0; };
+        if (wait_all(&q_full, 0) && wait_all(&k_full[0], 0)) {
+            for (int m = 0; m < 2; ++m)
+                if (n_m[m] > 0) issue_s(m, 0, m == last_active(0));
         }
+        int stage = 0, phase = 0;
+#pragma unroll 1
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int nstage = stage + 1 == S ? 0 : stage + 1, nphase = stage + 1 == S ? phase ^ 1 : phase;
+            for (int m = 0; m < 2 && ok; ++m) {
+                if (j >= n_m[m]) continue;
+                if (!wait_all(&p_full[m], j & 1)) break;
+                if (m == first_active(j) && !wait_all(&v_full[stage], phase)) break;
+                issue_o(m, stage, j == 0, j == n_m[m] - 1, m == last_active(j));
+                if (j + 1 < n_m[m]) {
+                    if (m == first_active(j + 1) && !wait_all(&k_full[nstage], nphase)) break;
+                    issue_s(m, nstage, m == last_active(j + 1));
+                }
+            }
+            stage = nstage; phase = nphase;
+        }
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 9);
     } else {
         // ---------------- softmax: thread = row ----------------
         const int m = warp >> 2;                                  // row tile
@@ -250,9 +256,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (kj > row_pos || kj < row_lo) sr[c] = __float_as_uint(-INFINITY);
                 }
             }
-            float rmax = -INFINITY;
+            // eight chains side by side: one chain of 128 dependent operations would take their latency 128 times
+            float mx[8];
 #pragma unroll
-            for (int c = 0; c < PT_KEYS; ++c) rmax = fmaxf(rmax, __uint_as_float(sr[c]));
+            for (int i = 0; i < 8; ++i) mx[i] = __uint_as_float(sr[i]);
+#pragma unroll
+            for (int c = 8; c < PT_KEYS; ++c) mx[c & 7] = fmaxf(mx[c & 7], __uint_as_float(sr[c]));
+            const float rmax = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
             const float cand = fmaxf(m_ref, rmax * p.scale_log2);  // scale > 0: the maximum commutes with it
             const bool grow = cand > m_ref + ATT_RESCALE_STEP;      // also true for -inf -> finite
             if (__any_sync(0xffffffffu, grow)) {
@@ -273,6 +283,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             // exp2(s * scale - m); a row that has seen nothing yet has m = -inf and only -inf scores: exp2(-inf - 0) = 0
             const float mref = m_ref == -INFINITY ? 0.f : m_ref;
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < PT_KEYS; c += 32) {
                 uint32_t pk[16];
@@ -280,11 +291,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = 0; i < 16; ++i) {
                     const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c + 2 * i]), p.scale_log2, -mref));
                     const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 2 * i + 1]), p.scale_log2, -mref));
-                    l += p0 + p1;
+                    ls[i & 3] += p0 + p1;
                     pk[i] = pack_bf16(p0, p1);
                 }
                 tc_tmem_st16(s_addr + (c >> 1), pk);
             }
+            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             // Value rows of keys that nobody may see (before the first visible run, after the last key) hold whatever
             // their page holds, and 0 x NaN is NaN: this group clears them once the tile has landed and before it
             // lets its product start.  Only the first and the last tile of the block have such rows.
