@@ -18,10 +18,13 @@ from . import kernels as K
 from . import library as _l
 from .library import check
 
-# Which kernel prompt portions run on: "auto" takes the tcgen05 kernel where it takes the shape and the step
-# has at least TC_MIN_TOKENS tokens, "tc" takes it wherever it takes the shape, "mma" never.
+# Which kernel prompt portions run on: "auto" gives the tcgen05 kernel the portions that fill its blocks well
+# (where it takes the shape) and the mma.sync kernel the rest, "tc" gives the tcgen05 kernel everything it
+# takes, "mma" nothing.
 PREFILL_KERNEL = os.environ.get("PRELUDE_PREFILL_ATTN", "auto")
-TC_MIN_TOKENS = int(os.environ.get("PRELUDE_PREFILL_TC_MIN_TOKENS", "1"))
+TC_MIN_FILL = float(os.environ.get("PRELUDE_PREFILL_TC_MIN_FILL", "0.5"))
+# Whether the single tokens of a mixed step run on the decode kernel (PRELUDE_DECODE_IN_MIXED=0: on the prompt kernels).
+DECODE_IN_MIXED = os.environ.get("PRELUDE_DECODE_IN_MIXED", "1") != "0"
 
 SM_COUNT = 148          # refreshed from the device at first use
 _sm_count_known = False
@@ -56,24 +59,50 @@ def decode_splits(n_tokens: int, n_kv_heads: int, head_dim: int, max_context: in
     return max(1, min(resident // blocks, tiles, 64))
 
 
-def _prefill_plan(batch, tpt: int):
-    """Tiles of ``tpt`` tokens per request, as device arrays (made once per step and tile size)."""
-    key = ("attn_tiles", tpt)
+def _prefill_plan(batch, tpt: int, min_len: int = 0, max_len: Optional[int] = None):
+    """Tiles of ``tpt`` tokens of the requests whose portion has min_len <= tokens (< max_len), as device
+    arrays (made once per step and choice)."""
+    key = ("attn_tiles", tpt, min_len, max_len)
     plan = batch.extras.get(key)
     if plan is None:
-        seqs, toks = [], []
+        seqs, toks = [np.zeros(0, dtype=np.int32)], [np.zeros(0, dtype=np.int32)]
         for r, n in enumerate(batch.q_lens.tolist()):
+            if n < min_len or (max_len is not None and n >= max_len):
+                continue
             starts = np.arange(0, n, tpt, dtype=np.int32)
             seqs.append(np.full(starts.shape, r, dtype=np.int32))
             toks.append(starts)
         seqs, toks = np.concatenate(seqs), np.concatenate(toks)
-        # longest tiles first: a tile late in a portion walks more keys
-        order = np.argsort(-(toks + batch.q_start_host[seqs]), kind="stable")
-        host = torch.from_numpy(np.stack([seqs[order], toks[order]]))
-        dev = host.to(batch.token_ids.device, non_blocking=True)
-        plan = (dev[0], dev[1], int(seqs.shape[0]))
+        if seqs.shape[0] == 0:
+            plan = (None, None, 0)
+        else:
+            # longest tiles first: a tile late in a portion walks more keys
+            order = np.argsort(-(toks + batch.q_start_host[seqs]), kind="stable")
+            host = torch.from_numpy(np.stack([seqs[order], toks[order]]))
+            dev = host.to(batch.token_ids.device, non_blocking=True)
+            plan = (dev[0], dev[1], int(seqs.shape[0]))
         batch.extras[key] = plan
     return plan
+
+
+def _single_token_runs(batch):
+    """(first token, tokens, longest context) of every run of consecutive requests that bring one token each."""
+    runs = batch.extras.get("single_token_runs")
+    if runs is None:
+        runs = []
+        single = batch.q_lens == 1
+        r, R = 0, int(single.shape[0])
+        while r < R:
+            if not single[r]:
+                r += 1
+                continue
+            e = r
+            while e < R and single[e]:
+                e += 1
+            runs.append((int(batch.q_lens[:r].sum()), e - r, int(batch.kv_len_host[r:e].max())))
+            r = e
+        batch.extras["single_token_runs"] = runs
+    return runs
 
 
 def tensor_core_shape_ok(n_heads: int, n_kv_heads: int, head_dim: int, decode: bool, page_size: int = 16) -> bool:
@@ -96,37 +125,53 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     lib = _l.library()
     stream = torch.cuda.current_stream().cuda_stream
     win = int(window) if window else 0
-    if batch.decode_only:
-        max_ctx = batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size
+    swizzled = 1 if K.kv_swizzled(q.dtype, D) else 0
+
+    def decode(t0: int, n: int, max_ctx: int) -> None:
+        """Tokens t0 .. t0 + n of the batch, one per request, on the kernel that spreads a token's keys over blocks."""
         if window:
             max_ctx = min(max_ctx, window + 64)
-        splits = decode_splits(T, nKV, D, max_ctx, q.device)
-        if T * nKV > (1 << 16):
+        splits = decode_splits(n, nKV, D, max_ctx, q.device)
+        if n * nKV > (1 << 16):
             splits = 1
-        n = lib.pb_attention_decode_scratch_floats(T, nH, D, splits)
-        scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
-        counters = _decode_counters(q.device) if n else None
+        floats = lib.pb_attention_decode_scratch_floats(n, nH, D, splits)
+        scratch = torch.empty(floats, dtype=torch.float32, device=q.device) if floats else None
+        counters = _decode_counters(q.device) if floats else None
         check(lib.pb_attention_decode_bf16(
-            q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
-            batch.positions.data_ptr(), batch.token_seq.data_ptr(), page_size, num_pages, T, nH, nKV, D, float(scale),
-            win, 1 if K.kv_swizzled(q.dtype, D) else 0, splits, None if scratch is None else scratch.data_ptr(),
-            None if counters is None else counters.data_ptr(), batch.status.data_ptr(), stream),
-            "attention_decode")
+            q[t0:t0 + n].data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out[t0:t0 + n].data_ptr(), table.data_ptr(),
+            table.shape[1], batch.positions[t0:t0 + n].data_ptr(), batch.token_seq[t0:t0 + n].data_ptr(), page_size, num_pages,
+            n, nH, nKV, D, float(scale), win, swizzled, splits, None if scratch is None else scratch.data_ptr(),
+            None if counters is None else counters.data_ptr(), batch.status.data_ptr(), stream), "attention_decode")
+
+    if batch.decode_only:
+        decode(0, T, batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size)
         return out
-    swizzled = 1 if K.kv_swizzled(q.dtype, D) else 0
-    if PREFILL_KERNEL != "mma" and lib.pb_attention_prefill_tc_supported(nH, nKV, D, page_size, swizzled) \
-            and (PREFILL_KERNEL == "tc" or T >= TC_MIN_TOKENS):
-        tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, lib.pb_attention_prefill_tc_tile_tokens(nH, nKV))
-        check(lib.pb_attention_prefill_tc_bf16(
+    # A mixed step: runs of requests with a single token each (decode steps beside prompt portions) go to the decode
+    # kernel, as they would in a step of their own, where that kernel takes the shape.
+    mma_min = 0
+    if DECODE_IN_MIXED and tensor_core_shape_ok(nH, nKV, D, True, page_size):
+        for t0, n, max_ctx in _single_token_runs(batch):
+            decode(t0, n, max_ctx)
+        mma_min = 2
+    # The tcgen05 kernel works on 256 query rows at a time and pays for all of them: it takes the portions that
+    # fill at least TC_MIN_FILL of a block's tokens, the mma.sync kernel (64 rows at a time) the shorter ones
+    # and the single tokens of a mixed step.  Both write disjoint rows of `out`.
+    tc_min = None
+    if PREFILL_KERNEL != "mma" and lib.pb_attention_prefill_tc_supported(nH, nKV, D, page_size, swizzled):
+        tc_tokens = lib.pb_attention_prefill_tc_tile_tokens(nH, nKV)
+        tc_min = max(mma_min, 1 if PREFILL_KERNEL == "tc" else max(1, int(tc_tokens * TC_MIN_FILL)))
+        tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, tc_tokens, tc_min, None)
+        if n_tiles:
+            check(lib.pb_attention_prefill_tc_bf16(
+                q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
+                batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+                tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
+                swizzled, batch.status.data_ptr(), stream), "attention_prefill_tc")
+    tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, 64 // (nH // nKV), mma_min, tc_min)
+    if n_tiles:
+        check(lib.pb_attention_prefill_bf16(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
             batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
             tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
-            swizzled, batch.status.data_ptr(), stream), "attention_prefill_tc")
-        return out
-    tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, 64 // (nH // nKV))
-    check(lib.pb_attention_prefill_bf16(
-        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
-        batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
-        tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
-        1 if K.kv_swizzled(q.dtype, D) else 0, batch.status.data_ptr(), stream), "attention_prefill")
+            swizzled, batch.status.data_ptr(), stream), "attention_prefill")
     return out

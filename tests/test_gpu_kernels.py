@@ -443,10 +443,48 @@ def _check_dispatch(requests, nH, nKV, D, page, window, seed=0, trimmed_below=No
                                            (4, 2, 64, 24), (8, 2, 128, 48), (4, 1, 128, 64), (6, 3, 64, 128),
                                            (4, 4, 192, 16), (4, 1, 128, 8), (2, 2, 256, 40)])
 @pytest.mark.parametrize("window", [None, 70])
-def test_attention_prefill_tensor_cores(nH, nKV, D, page, window):
-    # whole prompts, a portion that continues a cached prefix, single tokens in between, a two-token portion
+@pytest.mark.parametrize("kernel", ["auto", "mma"])
+def test_attention_prefill_tensor_cores(monkeypatch, nH, nKV, D, page, window, kernel):
+    # whole prompts, a portion that continues a cached prefix, single tokens in between, a two-token portion;
+    # "auto" takes the tcgen05 kernel where it takes the shape, "mma" keeps every shape on the mma.sync kernel
+    from prelude_b200.ops import attention
+    monkeypatch.setattr(attention, "PREFILL_KERNEL", kernel)
     requests = [(83, 83), (200, 37), (150, 1), (2, 2), (130, 129), (65, 1), (64, 64)]
     _check_dispatch(requests, nH, nKV, D, page, window)
+
+
+@pytest.mark.parametrize("nH,nKV,D,page", [(3, 3, 64, 8), (4, 2, 128, 16), (8, 2, 64, 32), (16, 2, 128, 64), (16, 1, 64, 128),
+                                           (32, 1, 128, 256), (2, 2, 128, 64), (32, 8, 128, 16)])
+@pytest.mark.parametrize("window", [None, 100, 300])
+def test_attention_prefill_tcgen05(monkeypatch, nH, nKV, D, page, window):
+    """The tcgen05 kernel alone, at every group size it takes (1 to 32 query heads per key/value head), both head
+    sizes and pages from 8 to 256 tokens: portions longer and shorter than a block's tokens, a long cached prefix,
+    portions that end one key before, at and after a tile's edge, and single tokens."""
+    from prelude_b200.ops import attention
+    from prelude_b200.ops import library as L
+    assert L.library().pb_attention_prefill_tc_supported(nH, nKV, D, page, 1)
+    monkeypatch.setattr(attention, "PREFILL_KERNEL", "tc")
+    requests = [(300, 300), (700, 90), (127, 127), (128, 128), (129, 129), (513, 1), (1000, 260), (5, 5), (257, 2)]
+    got_tc = _check_dispatch(requests, nH, nKV, D, page, window, seed=3)
+    monkeypatch.setattr(attention, "PREFILL_KERNEL", "mma")
+    got_mma = _check_dispatch(requests, nH, nKV, D, page, window, seed=3)
+    assert (got_tc.float() - got_mma.float()).abs().max() <= tol(torch.bfloat16, 4.0)
+
+
+def test_attention_prefill_tcgen05_refuses_what_it_does_not_take():
+    from prelude_b200.ops import library as L
+    lib = L.library()
+    assert not lib.pb_attention_prefill_tc_supported(6, 2, 128, 16, 1)       # three query heads per key/value head
+    assert not lib.pb_attention_prefill_tc_supported(8, 2, 96, 16, 1)        # head size
+    assert not lib.pb_attention_prefill_tc_supported(8, 2, 128, 24, 1)       # pages that do not tile 128 keys
+    assert not lib.pb_attention_prefill_tc_supported(8, 2, 128, 16, 0)       # pages that are not permuted
+    assert lib.pb_attention_prefill_tc_tile_tokens(32, 8) == 64
+    t = torch.zeros(64, dtype=torch.bfloat16, device=DEV)
+    i = torch.zeros(8, dtype=torch.int32, device=DEV)
+    code = lib.pb_attention_prefill_tc_bf16(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), i.data_ptr(), 1, i.data_ptr(),
+                                            i.data_ptr(), i.data_ptr(), i.data_ptr(), i.data_ptr(), i.data_ptr(), 1, 24, 1, 1, 8, 2,
+                                            128, 0.1, 0, 1, i.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert code != 0 and "not taken" in L.last_error()
 
 
 @pytest.mark.parametrize("nH,nKV,D,page", [(4, 2, 16, 4), (6, 2, 32, 8), (5, 1, 48, 16), (8, 8, 64, 16), (3, 3, 80, 16),
