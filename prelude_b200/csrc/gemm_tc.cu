@@ -7,12 +7,7 @@
 // A linear layer y = x W^T is A = x (128 tokens per tile), B = W (up to 256
 // features per tile), for prompt portions and for decode steps alike.  A decode
 // step has a handful of tokens: TMA fills the rows of the A tile that do not
-// exist with zeros, and the step is a stream over W.  The other orientation
-// (W as the 128-row operand, the batch as a 16-column B) was measured and
-// dropped: an MMA of 128 rows takes about 128 cycles however few columns it
-// has, so with 16 columns the tensor pipe consumes W at 28 bytes a cycle, no
-// faster than memory delivers it, while with 256 features per instruction it
-// consumes 64 bytes a cycle.
+// exist with zeros, and the step is a stream over W.
 // (The reference sends these products to DeepGEMM / CUTLASS / cuBLAS,
 // crates/prelude-cuda/src/ops/gemm.rs:35-137; its sm_100 path is
 // crates/prelude-cuda/deepgemm/src/sm100_bf16.cuh:10-205.)
@@ -170,36 +165,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer: reads shared and tensor memory only ----------------
-        if (lane == 0) {
-            const uint32_t idesc = tc_instr_desc(BN);
-            int fill = 0, seg = 0;
-            bool ok = true;
-            for (int it = my_begin; it < my_end && ok; ++seg) {
-                const int tile = it / p.kblocks;
-                const int seg_end = min(my_end, (tile + 1) * p.kblocks);
-                const int acc = seg & 1;
-                ok = tc_mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1);
+        // The whole warp walks the loop and waits; an elected lane issues (under elect.sync the descriptors stay in
+        // uniform registers; from a branch on the lane number every tcgen05.mma cost the thread about 100 cycles).
+        const uint32_t idesc = tc_instr_desc(BN);
+        int fill = 0, seg = 0;
+        bool ok = true;
+        for (int it = my_begin; it < my_end && ok; ++seg) {
+            const int tile = it / p.kblocks;
+            const int seg_end = min(my_end, (tile + 1) * p.kblocks);
+            const int acc = seg & 1;
+            ok = __all_sync(0xffffffffu, tc_mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1));
+            if (!ok) break;
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (int i = it; i < seg_end; ++i, ++fill) {
+                const int stage = fill % S::STAGES;
+                ok = __all_sync(0xffffffffu, tc_mbar_wait(&full_bar[stage], (fill / S::STAGES) & 1));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int i = it; i < seg_end; ++i, ++fill) {
-                    const int stage = fill % S::STAGES;
-                    ok = tc_mbar_wait(&full_bar[stage], (fill / S::STAGES) & 1);
-                    if (!ok) break;
-                    tc_fence_after();
+                if (tc_elect_one()) {
                     const unsigned char* sa = smem + stage * S::STAGE_BYTES;
                     const uint64_t da = tc_smem_desc(sa), db = tc_smem_desc(sa + TC_A_BYTES);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)                         // 32 bytes along K per instruction
                         tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (i > it || k > 0) ? 1u : 0u);
                     tc_commit(&empty_bar[stage]);                                // the stage is free when these finish
+                    if (i + 1 == seg_end) tc_commit(&acc_full[acc]);
                 }
-                if (!ok) break;
-                tc_commit(&acc_full[acc]);
-                it = seg_end;
+                __syncwarp();
             }
-            if (!ok && p.status) atomicExch(p.status, 9);
+            if (!ok) break;
+            it = seg_end;
         }
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 9);
     } else {
         // ---------------- epilogue: 4 warps, 128 accumulator rows ----------------
         pb_grid_dep_wait();                                                      // the output and the scratch may still be in use
