@@ -121,7 +121,7 @@ def build_engine(layers, max_running, num_pages):
     del tensors
     torch.cuda.empty_cache()
     return Engine(model, page_size=PAGE_SIZE, num_pages=num_pages, max_running_requests=max_running,
-                  max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN, cuda_graph=True, cuda_graph_max_bs=64), cfg
+                  max_num_batched_tokens=max(8192, PREFILL_TOKENS), max_model_len=CONTEXT_LEN, cuda_graph=True, cuda_graph_max_bs=64), cfg
 
 
 def weight_bytes_per_step(cfg):
@@ -238,7 +238,7 @@ def time_e2e(engine, cfg, batch, steps):
 
 
 def main():
-    global MODEL, PREFIX_LEN, CONTEXT_LEN
+    global MODEL, PREFIX_LEN, CONTEXT_LEN, PAGE_SIZE, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -249,6 +249,8 @@ def main():
                     help="layer sizes of another Qwen3 dense model (the headline run is 4b)")
     ap.add_argument("--prefix-len", type=int, default=PREFIX_LEN, help="tokens every request holds before the timed decode steps")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt (the contract's is 2,048)")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -263,7 +265,9 @@ def main():
     if args.model_size != "4b":
         MODEL = dict(QWEN3_4B, **OTHER_SIZES[args.model_size])
     PREFIX_LEN = args.prefix_len
-    CONTEXT_LEN = max(CONTEXT_LEN, PREFIX_LEN + args.steps + args.warmup + 64)
+    PAGE_SIZE = args.page_size
+    PREFILL_TOKENS = args.prefill_tokens
+    CONTEXT_LEN = max(CONTEXT_LEN, PREFIX_LEN + args.steps + args.warmup + 64, PREFILL_TOKENS + 64)
     args.layers = args.layers or MODEL["num_hidden_layers"]
     import torch
     pk = peaks()

@@ -107,25 +107,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (warp == 8) {
         // ---------------- loads ----------------
-        if (lane == 0) {
-            const int32_t* table = p.block_table + (size_t)p.token_seq[q_base + tok0] * p.table_stride;
-            const int runs = PT_KEYS / pp.kv_rows;
-            const int safe_pi = p_max / ps;                      // a page this request holds for sure
-            // the page and the row in it where the u-th run of key tile j starts; runs without a visible key
-            // are read from the safe page instead (their probabilities are zero, the values only have to be finite)
-            auto locate = [&](int j, int u, int& page, int& row) {
-                int j0 = (kt0 + j) * PT_KEYS + u * pp.kv_rows;
-                int pi = j0 / ps;
-                row = j0 - pi * ps;
-                if (j0 > p_max || j0 + pp.kv_rows <= lo) { pi = safe_pi; row = 0; }
-                page = table[pi];
-                if (page < 0 || page >= p.num_pages) {           // never read outside the pool; the step is reported as bad
-                    page = 0;
-                    if (p.status) atomicExch(p.status, 6);
-                }
-            };
-            // q and the newest keys and values are the output of the kernel before this one
-            pb_grid_dep_wait();
+        // The whole warp walks the loop.  It keeps 32 consecutive entries
+        // of the request's block table in registers, one per lane, and the 32 after them: a page number is then a
+        // shuffle away, not a trip to memory per copy.
+        const int32_t* table = p.block_table + (size_t)p.token_seq[q_base + tok0] * p.table_stride;
+        const int runs = PT_KEYS / pp.kv_rows;
+        const int last_pi = p_max / ps;                          // the last page the block reads; the request holds it for sure
+        const int hi_run = p_max / pp.kv_rows * pp.kv_rows;      // first key of the last run that holds a visible key
+        int win_pi = (kt0 * PT_KEYS) / ps;                       // table index that lane 0 of `cur` holds
+        int cur = table[min(win_pi + lane, last_pi)], nxt = table[min(win_pi + 32 + lane, last_pi)];
+        // The page and the row in it where the u-th run of key tile j starts.  Runs without a visible key (before the
+        // window, after the last key) are read from the nearest run that has one: their probabilities are zero, and
+        // the value rows are cleared by the softmax threads.
+        auto locate = [&](int j, int u, int& page, int& row) {
+            int j0 = (kt0 + j) * PT_KEYS + u * pp.kv_rows;
+            j0 = min(max(j0, lo_run), hi_run);
+            const int pi = j0 / ps;
+            row = j0 - pi * ps;
+            const int idx = pi - win_pi;                         // 0 .. 47: the tile starts inside `cur` and spans at most 16 pages
+            const int a = __shfl_sync(0xffffffffu, cur, idx & 31), b = __shfl_sync(0xffffffffu, nxt, idx & 31);
+            page = idx < 32 ? a : b;
+            if (page < 0 || page >= p.num_pages) {               // never read outside the pool; the step is reported as bad
+                page = 0;
+                if (p.status) atomicExch(p.status, 6);
+            }
+        };
+        // q and the newest keys and values are the output of the kernel before this one
+        pb_grid_dep_wait();
+        if (tc_elect_one()) {
             mbar_arrive_expect_tx(&q_full, T::Q_BYTES);
             for (int i = 0; i < 256 / pp.q_rows; ++i) {
                 const int R0 = i * pp.q_rows, hg = R0 / TOK, tl0 = R0 - hg * TOK;
@@ -134,36 +143,41 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int h = 0; h < T::HALVES; ++h)
                     tc_tma_load_3d(dst + h * PT_SLAB, &map_q, h * 64, kvh * G + hg, q_base + tok0 + tl0, &q_full);
             }
-            bool ok = true;
-            int stage = 0, phase = 0;
-#pragma unroll 1
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                unsigned char* sK = sKV + stage * 2 * T::TILE_BYTES;
-                unsigned char* sV = sK + T::TILE_BYTES;
-                ok = mbar_wait_bounded(&k_empty[stage], phase ^ 1);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&k_full[stage], T::TILE_BYTES);
-                for (int u = 0; u < runs; ++u) {
-                    int page, row;
-                    locate(j, u, page, row);
-#pragma unroll
-                    for (int h = 0; h < T::HALVES; ++h)
-                        tc_tma_load_5d(sK + h * PT_SLAB + u * pp.kv_rows * 128, &map_k, 0, h, row, kvh, page, &k_full[stage]);
-                }
-                ok = mbar_wait_bounded(&v_empty[stage], phase ^ 1);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&v_full[stage], T::TILE_BYTES);
-                for (int u = 0; u < runs; ++u) {
-                    int page, row;
-                    locate(j, u, page, row);
-#pragma unroll
-                    for (int h = 0; h < T::HALVES; ++h)
-                        tc_tma_load_5d(sV + h * PT_SLAB + u * pp.kv_rows * 128, &map_v, 0, h, row, kvh, page, &v_full[stage]);
-                }
-                if (++stage == S) { stage = 0; phase ^= 1; }
-            }
-            if (!ok && p.status) atomicExch(p.status, 7);
         }
+        __syncwarp();
+        bool ok = true;
+        int stage = 0, phase = 0;
+#pragma unroll 1
+        for (int j = 0; j < n_tiles; ++j) {
+            unsigned char* sK = sKV + stage * 2 * T::TILE_BYTES;
+            unsigned char* sV = sK + T::TILE_BYTES;
+            while (((kt0 + j) * PT_KEYS) / ps - win_pi >= 32) {  // slide the window of table entries
+                cur = nxt;
+                win_pi += 32;
+                nxt = table[min(win_pi + 32 + lane, last_pi)];
+            }
+            // lane u brings the u-th run of the tile, its keys and then its values: the copies of a tile are issued
+            // side by side, not one after the other
+            int page, row;
+            locate(j, lane < runs ? lane : 0, page, row);
+#pragma unroll 1
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                uint64_t* full = kv ? &v_full[stage] : &k_full[stage];
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(kv ? &v_empty[stage] : &k_empty[stage], phase ^ 1));
+                if (!ok) break;
+                if (lane == 0) mbar_arrive_expect_tx(full, T::TILE_BYTES);
+                __syncwarp();
+                if (lane < runs) {
+#pragma unroll
+                    for (int h = 0; h < T::HALVES; ++h)
+                        tc_tma_load_5d((kv ? sV : sK) + h * PT_SLAB + lane * pp.kv_rows * 128, kv ? &map_v : &map_k, 0, h, row, kvh, page, full);
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+            if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 7);
     } else if (warp == 9) {
         // ---------------- products: reads shared and tensor memory only ----------------
         // The whole warp walks the loop and waits; one elected lane issues.  (Issued from a branch on the lane
