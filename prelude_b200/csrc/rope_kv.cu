@@ -104,8 +104,6 @@ __global__ void qknorm_rope_kvwrite_kernel(
     }
 }
 
-#define ROPE_HEADS_MIN_TOKENS 128   // from this many tokens on, a lane walks several heads
-
 // The vector kernel: LANES = head_dim / 8 lanes per (token, head), 8 elements each.
 template <int LANES>
 __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
@@ -214,130 +212,6 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     }
 }
 
-// The vector kernel for steps with many tokens: LANES lanes per token and block of HPT heads.  A lane keeps its
-// 16-byte chunk's norm scales and rotation factors in registers and walks the HPT heads with them (the kernel above
-// fetches 96 bytes of tables for every 16 bytes of data); the rows of all its heads are loaded before the first is
-// worked on.
-template <int LANES, int HPT>
-__global__ void __launch_bounds__(256) qknorm_rope_kvwrite_heads_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    long long token_stride, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
-    __nv_bfloat16* __restrict__ v_pages, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int max_positions,
-    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
-    const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
-    int n_tokens, int n_heads, int n_kv_heads, int write_kv, int swizzle, int* __restrict__ status) {
-    pb_grid_dep_launch();
-    constexpr int D = LANES * 8;
-    const int heads_per_token = n_heads + (write_kv ? 2 * n_kv_heads : 0);
-    const int blocks_per_token = (heads_per_token + HPT - 1) / HPT;
-    const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;     // (token, block of heads) of this lane
-    const int c = threadIdx.x % LANES;                                                       // its 16-byte chunk
-    const bool live = group < (long long)n_tokens * blocks_per_token;
-    // lanes without a row keep going (the shuffles below are warp-wide) on token 0 and store nothing
-    const int t = live ? (int)(group / blocks_per_token) : 0;
-    const int slot0 = live ? (int)(group % blocks_per_token) * HPT : 0;
-    // everything that depends on the step's index arrays and the model's tables alone is fetched before the wait for
-    // the kernel ahead (which writes q, k and v)
-    const int pos = positions[t];
-    bool kv_ok = false;
-    size_t kv_row = 0;                                                                       // element offset of the token's row of head 0 in a page
-    int in_page = 0;
-    if (write_kv) {
-        const int page = pos >= 0 ? block_table[(size_t)token_seq[t] * table_stride + pos / page_size] : -1;
-        if (page < 0 || page >= num_pages) {
-            if (live && c == 0 && status) atomicExch(status, 2);
-        } else {
-            kv_ok = true;
-            in_page = pos % page_size;
-            kv_row = ((size_t)page * n_kv_heads * page_size + in_page) * D;
-        }
-    }
-    const int cc = swizzle ? (c ^ (in_page & 7)) : c;                                        // chunks of a page row may be permuted
-    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f), zero = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 qw0 = one, qw1 = one, kw0 = one, kw1 = one;
-    if (q_weight != nullptr) { qw0 = *reinterpret_cast<const float4*>(q_weight + c * 8); qw1 = *reinterpret_cast<const float4*>(q_weight + c * 8 + 4); }
-    if (k_weight != nullptr) { kw0 = *reinterpret_cast<const float4*>(k_weight + c * 8); kw1 = *reinterpret_cast<const float4*>(k_weight + c * 8 + 4); }
-    // rotation: element j of the first half pairs with j + half; the partner chunk sits half / 8 lanes away
-    const int half = (cos_table != nullptr) ? rotary_dim / 2 : 0;
-    const int hc = half / 8;                                                                 // chunks per half (0: no rotation)
-    const bool first = c < hc, second = c >= hc && c < 2 * hc;
-    const bool in_rotary = first || second;
-    bool pos_ok = true;
-    float4 c0 = one, c1 = one, s0 = zero, s1 = zero;
-    if (in_rotary) {
-        if (pos < 0 || pos >= max_positions) {
-            if (live && c == 0 && status) atomicExch(status, 3);
-            pos_ok = false;
-        } else {
-            const int j0 = (first ? c : c - hc) * 8;
-            const float* cp = cos_table + (size_t)pos * half + j0;
-            const float* sp = sin_table + (size_t)pos * half + j0;
-            c0 = *reinterpret_cast<const float4*>(cp); c1 = *reinterpret_cast<const float4*>(cp + 4);
-            s0 = *reinterpret_cast<const float4*>(sp); s1 = *reinterpret_cast<const float4*>(sp + 4);
-        }
-    }
-    const int partner = first ? c + hc : (second ? c - hc : c);
-    const int src_lane = (threadIdx.x & 31) - c + partner;
-    pb_grid_dep_wait();
-    uint4 raw[HPT];
-#pragma unroll
-    for (int i = 0; i < HPT; ++i) {
-        const int slot = slot0 + i;
-        raw[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (live && slot < heads_per_token) {
-            const bool is_q = slot < n_heads, is_k = !is_q && slot < n_heads + n_kv_heads;
-            const int h = is_q ? slot : (is_k ? slot - n_heads : slot - n_heads - n_kv_heads);
-            raw[i] = *reinterpret_cast<const uint4*>((is_q ? q : is_k ? k : v) + (size_t)t * token_stride + (size_t)h * D + c * 8);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < HPT; ++i) {
-        const int slot = slot0 + i;
-        const bool have = live && slot < heads_per_token;
-        const bool is_q = slot < n_heads, is_k = !is_q && slot < n_heads + n_kv_heads;
-        const int h = is_q ? slot : (is_k ? slot - n_heads : slot - n_heads - n_kv_heads);
-        if (have && !is_q && !is_k && kv_ok)                                                 // values: plain copy
-            *reinterpret_cast<uint4*>(v_pages + kv_row + (size_t)h * page_size * D + cc * 8) = raw[i];
-        // no `continue`: the lanes of this warp that hold q or k rows need all lanes at the shuffles
-        float x[8];
-        {
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h2[e]); x[2 * e] = f.x; x[2 * e + 1] = f.y; }
-        }
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
-#pragma unroll
-        for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // over the lanes of the row
-        if ((is_q && q_weight != nullptr) || (is_k && k_weight != nullptr)) {
-            const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-            const float4 w0 = is_q ? qw0 : kw0, w1 = is_q ? qw1 : kw1;
-            x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
-            x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
-        }
-        float y[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = __shfl_sync(0xffffffffu, x[e], src_lane);
-        if (in_rotary) {
-            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-            for (int e = 0; e < 8; ++e) x[e] = first ? x[e] * cs[e] - y[e] * sn[e] : x[e] * cs[e] + y[e] * sn[e];
-        }
-        if (have && (is_q || is_k) && pos_ok && (is_q || kv_ok)) {       // a lane that rotates stores nothing at a bad position
-            uint4 out;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
-            __nv_bfloat16* dst = is_q ? q_out + ((size_t)t * n_heads + h) * D + c * 8
-                                      : k_pages + kv_row + (size_t)h * page_size * D + cc * 8;
-            *reinterpret_cast<uint4*>(dst) = out;
-        }
-    }
-}
-
 template <int LANES, typename... Args>
 static void launch_rope_vec(long long rows, cudaStream_t stream, Args... args) {
     const int threads = 256;
@@ -372,22 +246,6 @@ PB_API int pb_qknorm_rope_kvwrite(
     if (dtype == PB_BF16 && pow2 && rot_ok && aligned && warps * (head_dim / 8) < (1ll << 38)) {
         typedef const __nv_bfloat16* CB;
         typedef __nv_bfloat16* B;
-        // many tokens: the kernel that walks 8 heads per lane
-#define PB_ROPE_HEADS(L)                                                                                                \
-        do {                                                                                                            \
-            const long long groups = (long long)n_tokens * ((n_heads + (write_kv ? 2 * n_kv_heads : 0) + 7) / 8);      \
-            pb_launch(qknorm_rope_kvwrite_heads_kernel<L, 8>, dim3((unsigned)((groups * L + 255) / 256)), dim3(256), 0, \
-                      stream, (CB)q, (CB)k, (CB)v, token_stride, (B)q_out, (B)k_pages, (B)v_pages, q_weight, k_weight,  \
-                      eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq, block_table,          \
-                      table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, write_kv, swizzle, status);    \
-        } while (0)
-        if (n_tokens >= ROPE_HEADS_MIN_TOKENS && head_dim >= 64) {
-            if (head_dim == 64) PB_ROPE_HEADS(8);
-            else if (head_dim == 128) PB_ROPE_HEADS(16);
-            else PB_ROPE_HEADS(32);
-            PB_CHECK_LAUNCH("qknorm_rope_kvwrite");
-            return 0;
-        }
 #define PB_ROPE_VEC(L)                                                                                                  \
         launch_rope_vec<L>(warps, stream, (CB)q, (CB)k, (CB)v, token_stride, (B)q_out, (B)k_pages, (B)v_pages, q_weight,   \
                            k_weight, eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq,           \
@@ -399,7 +257,6 @@ PB_API int pb_qknorm_rope_kvwrite(
         else if (head_dim == 128) PB_ROPE_VEC(16);
         else PB_ROPE_VEC(32);
 #undef PB_ROPE_VEC
-#undef PB_ROPE_HEADS
         PB_CHECK_LAUNCH("qknorm_rope_kvwrite");
         return 0;
     }

@@ -248,68 +248,6 @@ def test_attention_finds_the_one_key_that_matters(dtype, where):
     assert hit == (where != "just_outside_window")
 
 
-@pytest.mark.parametrize("nH,nKV,D,rot", [(8, 2, 128, 128), (4, 4, 64, 32), (2, 1, 256, 256), (32, 8, 128, 128), (6, 2, 128, 64),
-                                          (5, 1, 64, 64), (3, 3, 128, 0)])
-@pytest.mark.parametrize("norm", [True, False])
-def test_qknorm_rope_kvwrite_many_tokens(nH, nKV, D, rot, norm):
-    """A step with hundreds of tokens takes the kernel in which a lane walks eight heads: two requests, one of them
-    continuing at position 5, head counts that do not fill the last block of eight, pages of 16 in a shuffled pool."""
-    dtype, page, eps, theta = torch.bfloat16, 16, 1e-6, 1000000.0
-    lens, starts = [200, 100], [5, 0]
-    T = sum(lens)
-    qkv = rnd(T, (nH + 2 * nKV) * D, dtype=dtype, seed=1)
-    qw, kw = (1 + 0.2 * rnd(D, seed=2), 1 + 0.2 * rnd(D, seed=3)) if norm else (None, None)
-    cos = sin = None
-    if rot:
-        inv = torch.tensor([1.0 / theta ** (i / rot) for i in range(0, rot, 2)], dtype=torch.float64).float()
-        ang = torch.arange(256, dtype=torch.float32)[:, None] * inv[None]
-        cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
-    positions = torch.cat([torch.arange(s0, s0 + n) for s0, n in zip(starts, lens)]).to(torch.int32).to(DEV)
-    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).to(torch.int32).to(DEV)
-    num_pages = 40
-    perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(4)).tolist()
-    table = torch.full((2, 16), -1, dtype=torch.int32)
-    for i, (s0, n) in enumerate(zip(starts, lens)):
-        for pi in range(-(-(s0 + n) // page)):
-            table[i, pi] = perm.pop()
-    table = table.to(DEV)
-    kp = torch.zeros(num_pages, nKV, page, D, dtype=dtype, device=DEV)
-    vp = torch.zeros_like(kp)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    q_out = K().qknorm_rope_kvwrite(qkv, nH, nKV, D, qw, kw, eps, cos, sin, rot, positions, seq, table, kp, vp, True, status)
-    assert int(status.item()) == 0
-
-    def plain(x, w):
-        x = x.float()
-        if w is not None:
-            x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
-        if rot:
-            c, s_ = cos[positions.long()][:, None, :], sin[positions.long()][:, None, :]
-            x1, x2, rest = x[..., :rot // 2], x[..., rot // 2:rot], x[..., rot:]
-            x = torch.cat([x1 * c - x2 * s_, x2 * c + x1 * s_, rest], -1)
-        return x
-    q = qkv[:, :nH * D].reshape(T, nH, D)
-    k = qkv[:, nH * D:(nH + nKV) * D].reshape(T, nKV, D)
-    v = qkv[:, (nH + nKV) * D:].reshape(T, nKV, D)
-    assert (q_out.float() - plain(q, qw)).abs().max() <= tol(dtype, 4.0)
-    want_k = plain(k, kw)
-    written = torch.zeros(num_pages, page, dtype=torch.bool)
-    for t in range(T):
-        pos, r = int(positions[t]), int(seq[t])
-        pg = int(table[r, pos // page])
-        assert (_get(kp, pg, pos % page).float() - want_k[t]).abs().max() <= tol(dtype, 4.0), t
-        assert torch.equal(_get(vp, pg, pos % page), v[t]), t
-        written[pg, pos % page] = True
-    unwritten = ~written.to(DEV)[:, None, :].expand(-1, nKV, -1)
-    assert float(kp[unwritten].abs().max()) == 0 and float(vp[unwritten].abs().max()) == 0
-    # a position beyond the tables and a page that the request does not hold are reported, and nothing is written for them
-    bad = positions.clone()
-    bad[7] = 100000
-    status.zero_()
-    K().qknorm_rope_kvwrite(qkv, nH, nKV, D, qw, kw, eps, cos, sin, rot, bad, seq, table, kp.clone(), vp.clone(), True, status)
-    assert int(status.item()) in (2, 3)
-
-
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("nH,nKV,D,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 1, 48, 48), (8, 2, 128, 128),
                                           (3, 3, 80, 32), (2, 1, 256, 256), (2, 2, 64, 0), (4, 2, 128, 64),
