@@ -123,7 +123,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                                      batch.status)
     out = torch.empty_like(q)
     lib = _l.library()
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = _l.current_stream_ptr(q.device)
     win = int(window) if window else 0
     swizzled = 1 if K.kv_swizzled(q.dtype, D) else 0
 

@@ -26,7 +26,7 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _l.current_stream_ptr()
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:

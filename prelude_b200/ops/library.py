@@ -117,6 +117,15 @@ def last_error() -> str:
 launch_count = 0     # launcher calls so far in this process (a launcher issues one kernel)
 
 
+def current_stream_ptr(device=None) -> int:
+    """The raw handle of the current CUDA stream of ``device`` (the current device if None).  One call into torch's
+    C module: the launch path asks for it several times per layer, and ``torch.cuda.current_stream()`` costs
+    about 10 microseconds a call."""
+    import torch
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    return torch._C._cuda_getCurrentRawStream(index)
+
+
 def check(code: int, what: str) -> None:
     global launch_count
     launch_count += 1

@@ -64,7 +64,7 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     check(_l.library().pb_gemm_stream_bf16(
         x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), M, N, Kdim,
         x.stride(0), weight.stride(0), N, 1 if out.dtype == torch.float32 else 0, splits, M * N, 1 if gated else 0,
-        tc_status(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream), "gemm_stream")
+        tc_status(x.device).data_ptr(), _l.current_stream_ptr(x.device)), "gemm_stream")
     return out
 
 
@@ -120,7 +120,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] 
     check(lib.pb_gemm_tc_bf16(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(),
                               M, N, Kdim, x.stride(0), weight.stride(0), out.stride(0), 1,
                               1 if out_dtype == torch.float32 else 0, scratch.data_ptr(), tc_status(x.device).data_ptr(),
-                              torch.cuda.current_stream().cuda_stream), "gemm_tc")
+                              _l.current_stream_ptr(x.device)), "gemm_tc")
     return out
 
 
