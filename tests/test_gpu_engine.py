@@ -20,6 +20,7 @@ REQUESTS = {
     "B": {"b2": 2, "b9": 9, "b31": 31, "b64": 64, "b150": 150},
     "C": {"c40": 40, "c33": 33, "c129": 129},
     "D": {"d3": 3, "d70": 70, "d200": 200},
+    "E": {"e2": 2, "e45": 45, "e130": 130, "e300": 300},
 }
 
 
@@ -56,14 +57,14 @@ def _runner(folder, dtype, page_size, num_pages):
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
-    for which in "ABCD":
+    for which in "ABCDE":
         for dtype in (torch.float32, torch.bfloat16):
             out[(which, dtype)] = tiny.make_folder(root, which, dtype)
     return out
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
 def test_cuts_match_plain(folders, which, dtype, cut):
     folder = folders[(which, dtype)]

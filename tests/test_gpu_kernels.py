@@ -471,6 +471,15 @@ def test_attention_prefill_tcgen05(monkeypatch, nH, nKV, D, page, window):
     assert (got_tc.float() - got_mma.float()).abs().max() <= tol(torch.bfloat16, 4.0)
 
 
+@pytest.mark.parametrize("nH,nKV,D,page", [(32, 8, 128, 16), (4, 4, 64, 8), (16, 1, 128, 64)])
+@pytest.mark.parametrize("requests", [[(5, 5)], [(33, 33)], [(300, 3)], [(64, 64), (2, 2)]], ids=str)
+def test_attention_prefill_tcgen05_on_steps_with_few_tokens(monkeypatch, nH, nKV, D, page, requests):
+    # the query box of the tensor map is then taller than the query tensor
+    from prelude_b200.ops import attention
+    monkeypatch.setattr(attention, "PREFILL_KERNEL", "tc")
+    _check_dispatch(requests, nH, nKV, D, page, None)
+
+
 def test_attention_prefill_tcgen05_refuses_what_it_does_not_take():
     from prelude_b200.ops import library as L
     lib = L.library()

@@ -42,7 +42,7 @@ def _run_trace(folder, dtype, schedule, out_dir, max_tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["B", "C"])
+@pytest.mark.parametrize("which", ["B", "C", "E"])
 def test_trace_run_mixed_with_reused_pages(tmp_path, which, dtype):
     cfg = tiny.PARAMS[which][0]
     folder = tiny.make_folder(tmp_path, which, torch.float32 if dtype == "float32" else torch.bfloat16)

@@ -32,8 +32,17 @@ TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               max_position_embeddings=512, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
               attention_bias=False, use_sliding_window=False, hidden_act="silu")
 
+# sizes that the tcgen05 prompt-attention kernel takes (head size 64, four query heads per key/value head, pages of
+# 8 tokens): in the engine tests the long portions then run on it, the short ones and the single tokens beside them
+# on the other two attention kernels
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=700, hidden_size=160,
+              intermediate_size=416, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+              max_position_embeddings=1024, rope_theta=500000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+              attention_bias=False, use_sliding_window=False, hidden_act="silu")
+
 PARAMS = {"A": (TINY_A, dict(seed=0, std=0.02, norm_jitter=0.1), 4),
           "D": (TINY_D, dict(seed=3, std=0.02, norm_jitter=0.1), 16),
+          "E": (TINY_E, dict(seed=4, std=0.04, norm_jitter=0.2), 8),
           "B": (TINY_B, dict(seed=1, std=0.03, norm_jitter=0.2), 8),
           "C": (TINY_C, dict(seed=2, std=0.05, norm_jitter=0.3), 16)}
 
