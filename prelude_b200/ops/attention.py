@@ -134,14 +134,20 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         splits = decode_splits(n, nKV, D, max_ctx, q.device)
         if n * nKV > (1 << 16):
             splits = 1
-        floats = lib.pb_attention_decode_scratch_floats(n, nH, D, splits)
-        scratch = torch.empty(floats, dtype=torch.float32, device=q.device) if floats else None
-        counters = _decode_counters(q.device) if floats else None
+        # the partial results of the splits: one buffer per step and size, shared by the layers (a layer's attention
+        # has finished long before the next layer's starts)
+        key = ("attn_decode_scratch", n, nH, D, splits)
+        scratch = batch.extras.get(key)
+        if scratch is None:
+            floats = lib.pb_attention_decode_scratch_floats(n, nH, D, splits)
+            scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
+            batch.extras[key] = scratch
+        row = nH * D * q.element_size()
         check(lib.pb_attention_decode_bf16(
-            q[t0:t0 + n].data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out[t0:t0 + n].data_ptr(), table.data_ptr(),
-            table.shape[1], batch.positions[t0:t0 + n].data_ptr(), batch.token_seq[t0:t0 + n].data_ptr(), page_size, num_pages,
-            n, nH, nKV, D, float(scale), win, swizzled, splits, None if scratch is None else scratch.data_ptr(),
-            None if counters is None else counters.data_ptr(), batch.status.data_ptr(), stream), "attention_decode")
+            q.data_ptr() + t0 * row, k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr() + t0 * row, table.data_ptr(),
+            table.shape[1], batch.positions.data_ptr() + 4 * t0, batch.token_seq.data_ptr() + 4 * t0, page_size, num_pages,
+            n, nH, nKV, D, float(scale), win, swizzled, splits, scratch.data_ptr() if splits > 1 else None,
+            _decode_counters(q.device).data_ptr() if splits > 1 else None, batch.status.data_ptr(), stream), "attention_decode")
 
     if batch.decode_only:
         decode(0, T, batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size)
