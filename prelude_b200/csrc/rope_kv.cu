@@ -20,7 +20,8 @@
 // halves of a rotation pair sit in two lanes of the group and are exchanged by
 // a shuffle; every row is read once.  Norm weights and the tables may be null:
 // no norm, no rotation.  A page id outside [0, num_pages) is never written; the
-// kernel raises *status instead.
+// kernel raises *status instead.  A token whose token_seq entry is negative is a
+// padding row (a captured step is as long as its bucket): nothing is written for it.
 #include "common.cuh"
 
 template <typename T>
@@ -40,6 +41,7 @@ __global__ void qknorm_rope_kvwrite_kernel(
     if (warp_id >= (long long)n_tokens * heads_per_token) return;
     const int t = (int)(warp_id / heads_per_token);
     const int slot = (int)(warp_id % heads_per_token);
+    if (token_seq != nullptr && token_seq[t] < 0) return;      // a padding row of a captured step: nothing to do
     const int pos = positions[t];
 
     const T* src;
@@ -127,14 +129,15 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     // started: everything that depends on them alone is fetched before the wait for the kernel ahead (which
     // writes q, k and v).
     const int pos = positions[t];
+    const bool padding = token_seq != nullptr && token_seq[t] < 0;                           // a padding row of a captured step
     const bool is_q = slot < n_heads, is_k = !is_q && slot < n_heads + n_kv_heads;
     const int h = is_q ? slot : (is_k ? slot - n_heads : slot - n_heads - n_kv_heads);
     const __nv_bfloat16* src = (is_q ? q : is_k ? k : v) + (size_t)t * token_stride + (size_t)h * D + c * 8;
     __nv_bfloat16* dst = nullptr;
-    bool store = live;
+    bool store = live && !padding;
     if (is_q) {
         dst = q_out + ((size_t)t * n_heads + h) * D + c * 8;
-    } else {
+    } else if (!padding) {
         const int seq = token_seq[t];
         const int page = pos >= 0 ? block_table[(size_t)seq * table_stride + pos / page_size] : -1;
         if (page < 0 || page >= num_pages) {
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     const bool first = c < hc, second = c >= hc && c < 2 * hc;
     const bool rotates = (first || second) && (is_q || is_k);
     float4 c0 = make_float4(1.f, 1.f, 1.f, 1.f), c1 = c0, s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
-    if (rotates) {
+    if (rotates && !padding) {
         if (pos < 0 || pos >= max_positions) {
             if (live && c == 0 && status) atomicExch(status, 3);
             store = false;

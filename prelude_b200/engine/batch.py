@@ -60,6 +60,21 @@ class StepBatch:
     max_kv_len: int = 0
     decode_only: bool = False
     extras: Dict[str, object] = field(default_factory=dict)    # per-kernel plans made once per step
+    real_tokens: int = -1               # tokens that exist; a captured step is padded to n_tokens (-1: all exist)
+
+    @property
+    def n_real(self) -> int:
+        return self.n_tokens if self.real_tokens < 0 else self.real_tokens
+
+    def workspace(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor that lives as long as the step and is handed out again for the same name, shape and type:
+        what one layer's mixer puts there is dead by the time the next layer's asks (the stream orders them),
+        so the layers share it instead of allocating each their own."""
+        key = ("workspace", name, tuple(shape), dtype)
+        t = self.extras.get(key)
+        if t is None:
+            t = self.extras[key] = torch.empty(tuple(shape), dtype=dtype, device=self.token_ids.device)
+        return t
 
 
 def _ceil_div(a: int, b: int) -> int:

@@ -117,6 +117,8 @@ class Engine:
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self.cuda_graph = cuda_graph
         self.graphs = DecodeGraphs(self.runner, cuda_graph_max_bs) if cuda_graph else None
+        if cuda_graph:
+            self.runner.enable_step_graphs()
         # Runs of decode steps queued without the host in between (see _burst_length): up to this many
         self.decode_burst = max(1, int(decode_burst))
         self.burst_graphs = (DecodeGraphs(self.runner, cuda_graph_max_bs, self_feeding=True)

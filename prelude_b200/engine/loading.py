@@ -48,11 +48,14 @@ def build_model(spec: ModelSpec, store: WeightStore, dtype: Union[str, torch.dty
 
 
 def make_runner(model: DecoderModel, page_size: int = 16, num_pages: Optional[int] = None,
-                max_tokens: Optional[int] = None, max_slots: int = 256) -> ModelRunner:
-    """A cache of ``num_pages`` pages (or enough for ``max_tokens`` tokens) and the runner over it."""
+                max_tokens: Optional[int] = None, max_slots: int = 256,
+                max_request_tokens: Optional[int] = None) -> ModelRunner:
+    """A cache of ``num_pages`` pages (or enough for ``max_tokens`` tokens) and the runner over it.  With
+    ``max_request_tokens`` the block tables also live on the device (what captured steps read)."""
     if num_pages is None:
         if max_tokens is None:
             raise ValueError("give num_pages or max_tokens")
         num_pages = -(-max_tokens // page_size)
-    cache = CacheManager(model.cache_needs(), page_size, num_pages, max_slots, model.ctx.device, model.ctx.dtype)
+    cache = CacheManager(model.cache_needs(), page_size, num_pages, max_slots, model.ctx.device, model.ctx.dtype,
+                         max_request_tokens=max_request_tokens)
     return ModelRunner(model, cache)

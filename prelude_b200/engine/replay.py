@@ -34,7 +34,9 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, pag
     os.makedirs(out_dir, exist_ok=True)
     model = load_model(model_dir, dtype, device)
     # every live request's count is rounded up to a multiple of 64 by the caller; pages divide 64
-    runner = make_runner(model, page_size=page_size, num_pages=max(1, -(-max_tokens // page_size)), max_slots=64)
+    runner = make_runner(model, page_size=page_size, num_pages=max(1, -(-max_tokens // page_size)), max_slots=64,
+                         max_request_tokens=max_tokens)
+    runner.enable_step_graphs()               # as generation runs them: steps with prompt tokens replay captured pieces
     n = 0
     for line in lines:
         line = line.strip()

@@ -48,6 +48,21 @@ class ModelRunner:
         self.caches = cache.layer_caches(len(model.order))
         self.steps_run = 0
         self.last_batch: Optional[StepBatch] = None
+        self.step_graphs = None             # engine.step_graph.StepGraphs: prompt steps captured piece by piece
+        self.graph_steps_run = 0
+
+    def enable_step_graphs(self, max_tokens: Optional[int] = None) -> bool:
+        """Capture steps with prompt tokens piece by piece, up to ``max_tokens`` of them (default 1,024, or
+        PRELUDE_STEP_GRAPH_MAX_TOKENS: longer steps keep the GPU busy longer than the host needs to launch them
+        one kernel at a time, so capturing them gains nothing).  Needs the device-resident block tables;
+        PRELUDE_STEP_GRAPHS=0 turns it off."""
+        import os
+        from .step_graph import StepGraphs
+        if os.environ.get("PRELUDE_STEP_GRAPHS", "1") == "0" or not self.cache.device_tables:
+            return False
+        cap = int(os.environ.get("PRELUDE_STEP_GRAPH_MAX_TOKENS", "1024"))
+        self.step_graphs = StepGraphs(self, cap if max_tokens is None else max_tokens)
+        return True
 
     # -- room in the cache --------------------------------------------------------------
     def reserve(self, entries: Sequence[StepEntry]) -> List[int]:
@@ -90,10 +105,24 @@ class ModelRunner:
         items = [StepItem(e.request_id, e.tokens, s, e.want) for e, s in zip(entries, starts)]
         rids = [e.request_id for e in entries]
         spec = self.model.spec
-        batch = build_step_batch(items, self.cache.block_tables(rids), [self.cache.slot_of(r) for r in rids],
-                                 self.device, spec.vocab_size, spec.max_positions)
-        self.cache.zero_fresh_state()
-        logits = self.model.forward(batch, self.caches)
+        slots = [self.cache.slot_of(r) for r in rids]
+        n_tokens = sum(len(e.tokens) for e in entries)
+        sg = self.step_graphs
+        if (sg is not None and n_tokens > len(entries)
+                and sg.usable(n_tokens, len(entries), max(s + len(e.tokens) for e, s in zip(entries, starts)))):
+            # a step with prompt tokens, replayed from its captured pieces: same kernels, fixed buffers
+            graph = sg.get(n_tokens)
+            graph.load(items, slots, spec.vocab_size, spec.max_positions)
+            self.cache.flush_table_updates()
+            self.cache.zero_fresh_state()
+            logits = graph.run()
+            batch = graph.batch
+            self.graph_steps_run += 1
+        else:
+            batch = build_step_batch(items, self.cache.block_tables(rids), slots, self.device, spec.vocab_size,
+                                     spec.max_positions)
+            self.cache.zero_fresh_state()
+            logits = self.model.forward(batch, self.caches)
         for r in rids:
             self.cache.trim(r)
         self.steps_run += 1

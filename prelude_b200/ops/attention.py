@@ -113,15 +113,27 @@ def tensor_core_shape_ok(n_heads: int, n_kv_heads: int, head_dim: int, decode: b
 
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, group: int,
-                    scale: float, window: Optional[int]) -> torch.Tensor:
-    """q [T, nH, D] of the batch's tokens against the pages of cache group ``group``."""
+                    scale: float, window: Optional[int], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, nH, D] of the batch's tokens against the pages of cache group ``group``; the result goes to ``out``
+    when given.  While a step is being captured piece by piece (``batch.extras["recorder"]``), attention is what
+    the pieces are cut at: its grids depend on how the step's tokens are spread over requests, so it is launched
+    at every step anew, between the replays of the pieces."""
+    recorder = batch.extras.get("recorder")
+    if recorder is not None and recorder.capturing:
+        if out is None:
+            out = torch.empty_like(q)
+        recorder.run_between_pieces(lambda: paged_attention(q, k_pages, v_pages, batch, group, scale, window, out))
+        return out
     table = batch.block_tables[group]
     T, nH, D = q.shape
     num_pages, nKV, page_size, _ = k_pages.shape
+    if out is None:
+        out = torch.empty_like(q)
     if q.dtype != torch.bfloat16 or not tensor_core_shape_ok(nH, nKV, D, batch.decode_only, page_size):
-        return K.paged_attention_ref(q, k_pages, v_pages, batch.positions, batch.token_seq, table, scale, window,
-                                     batch.status)
-    out = torch.empty_like(q)
+        n = batch.n_real                                   # the rows after them are padding of a captured step
+        out[:n] = K.paged_attention_ref(q[:n], k_pages, v_pages, batch.positions[:n], batch.token_seq[:n], table, scale,
+                                        window, batch.status)
+        return out
     lib = _l.library()
     stream = _l.current_stream_ptr(q.device)
     win = int(window) if window else 0

@@ -146,8 +146,8 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
                         positions: torch.Tensor, token_seq: Optional[torch.Tensor],
                         block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
                         v_pages: Optional[torch.Tensor], write_kv: bool,
-                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q/k norm + rotation, q to a dense [T, nH, D] tensor, k and v into their pages.
+                        status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q/k norm + rotation, q to a dense [T, nH, D] tensor (``out`` if given), k and v into their pages.
 
     ``qkv`` is the merged projection [T, (nH + 2 nKV) D] (or [T, nH D] when
     nothing is written).  Pages are [num_pages, nKV, page_size, D].
@@ -162,7 +162,13 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
         raise KernelLibraryError(f"qknorm_rope_kvwrite: projection has {qkv.shape[1]} columns, needs {want}")
     esz = qkv.element_size()
     base = qkv.data_ptr()
-    q_out = torch.empty((T, n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    if out is None:
+        q_out = torch.empty((T, n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    else:
+        _need(out, "out", qkv.dtype)
+        if tuple(out.shape) != (T, n_heads, head_dim):
+            raise KernelLibraryError(f"qknorm_rope_kvwrite: out is {tuple(out.shape)}, q is {(T, n_heads, head_dim)}")
+        q_out = out
     max_pos, page_size, num_pages, stride = 0, 0, 0, 0
     if cos is not None:
         _need(cos, "cos", torch.float32)

@@ -92,10 +92,21 @@ class DecoderModel:
     def forward(self, batch, caches) -> torch.Tensor:
         """``caches[n]`` is the LayerCache that entry n of the order owns.
         Returns float32 logits [len(batch.logit_rows), vocab]."""
+        delta, res = self.forward_hidden(batch, caches)
+        return self.head_logits(delta, res, batch)
+
+    def forward_hidden(self, batch, caches):
+        """The layers: returns (delta, res), the last layer's output and the residual it has yet to be added to.
+        Every launch in here has the shape of the step's token count alone, except what a mixer runs through
+        ``batch.extras["recorder"]``; that is what lets a step be captured piece by piece."""
         res = K.embed_gather(batch.token_ids, self.embed)
         delta = None
         for call in self.order:
             delta = self.blocks[call.block].forward(delta, res, batch, caches[call.cache], call.writes_cache)
+        return delta, res
+
+    def head_logits(self, delta, res, batch) -> torch.Tensor:
+        """Final norm and output head at the rows whose logits are wanted."""
         if batch.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=res.device)
         x = self.final_norm.gather_add_forward(delta, res, batch.logit_rows)

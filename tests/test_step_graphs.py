@@ -1,0 +1,76 @@
+"""Steps with prompt tokens replayed from captured pieces: the same logits as the same steps launched kernel by
+kernel, through mixed schedules with so few pages that they are used again."""
+import pytest
+import torch
+
+import harness
+import tiny
+
+
+def test_buckets_cover_their_token_counts():
+    from prelude_b200.engine.step_graph import bucket_of
+    last = 0
+    for n in range(1, 9000):
+        b = bucket_of(n)
+        assert b >= n and b >= last and b - n < max(32, n // 4), (n, b)      # never more than a quarter of padding
+        last = b
+    assert bucket_of(1) == 32 and bucket_of(32) == 32 and bucket_of(33) == 64 and bucket_of(257) == 320
+    assert bucket_of(1024) == 1024 and bucket_of(1025) == 1152 and bucket_of(4097) == 4352
+
+
+def _runners(folder, dtype, page, graphs):
+    from prelude_b200.engine.loading import load_model, make_runner
+    model = load_model(folder, dtype, "cuda:0")
+    runner = make_runner(model, page_size=page, num_pages=40 * 8 // page + 8, max_slots=8, max_request_tokens=512)
+    if graphs:
+        assert runner.enable_step_graphs(512)
+    return runner
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which", ["B", "D", "E"])
+def test_captured_steps_give_the_logits_of_launched_steps(tmp_path, which, dtype):
+    cfg, _, page = tiny.PARAMS[which]
+    folder = tiny.make_folder(tmp_path, which, dtype)
+    reqs = {f"r{i}": tiny.random_ids(n, cfg["vocab_size"], 70 + i) for i, n in enumerate([70, 45, 133, 100, 64, 20])}
+    outs = {}
+    for graphs in (False, True):
+        runner = _runners(folder, dtype, page, graphs)
+        for rep in range(2):                   # the second pass replays what the first captured
+            outs[(graphs, rep)] = harness.run_schedule(runner, harness.mixed(reqs, max_live=4, seed=3 + rep))
+        runner.cache.check()
+        assert runner.cache.used_pages() == 0
+        if graphs:
+            assert runner.graph_steps_run > 0.5 * runner.steps_run
+            assert sum(g.replays for g in runner.step_graphs.graphs.values()) > 0.4 * runner.steps_run
+    for rep in range(2):
+        for key, row in outs[(False, rep)].items():
+            other = outs[(True, rep)][key]
+            if dtype == torch.float32:
+                assert torch.equal(row, other), key            # the same kernels in the same order on every row
+            else:
+                # a padded step may take another product kernel (more rows): rounding differs, nothing else
+                assert float((row - other).abs().max()) <= 3e-2 * float(row.abs().max()), key
+
+
+@pytest.mark.gpu
+def test_a_step_longer_than_the_limit_is_launched(tmp_path):
+    cfg, _, page = tiny.PARAMS["E"]
+    folder = tiny.make_folder(tmp_path, "E", torch.bfloat16)
+    from prelude_b200.engine.loading import load_model, make_runner
+    from prelude_b200.engine.runner import StepEntry
+    model = load_model(folder, torch.bfloat16, "cuda:0")
+    runner = make_runner(model, page_size=page, num_pages=100, max_slots=4, max_request_tokens=400)
+    assert runner.enable_step_graphs(64)
+    toks = tiny.random_ids(200, cfg["vocab_size"], 5)
+    a = runner.step([StepEntry("a", toks[:100], [99])])       # 100 tokens: over the limit of 64
+    assert runner.graph_steps_run == 0
+    b = runner.step([StepEntry("a", toks[100:150], [49])])    # 50 tokens: captured at 64
+    assert runner.graph_steps_run == 1 and sorted(runner.step_graphs.graphs) == [64]
+    c = runner.step([StepEntry("a", toks[150:151], [0])])     # a decode step is not a prompt step
+    assert runner.graph_steps_run == 1
+    assert a.shape == b.shape == c.shape == (1, cfg["vocab_size"])
+    # without the device-resident block tables there is nothing to capture against
+    plain = make_runner(model, page_size=page, num_pages=100, max_slots=4)
+    assert not plain.enable_step_graphs(64)
