@@ -160,6 +160,30 @@ class Engine:
                 done.append(bs)
         return done
 
+    def warmup_prompt_steps(self, token_counts: Optional[Sequence[int]] = None) -> List[int]:
+        """Capture the pieces of prompt steps for the buckets of the given token counts (default: every bucket up
+        to the limit) before a request needs them: the first step of a bucket records its pieces, which takes
+        tens of milliseconds.  Runs one dummy prompt per bucket; returns the buckets captured."""
+        from .step_graph import bucket_of
+        sg = self.runner.step_graphs
+        if sg is None:
+            return []
+        if token_counts is None:
+            token_counts, n = [], 1
+            while bucket_of(n) <= sg.max_tokens:
+                token_counts.append(bucket_of(n))
+                n = bucket_of(n) + 1
+        done = []
+        for n in sorted({bucket_of(int(t)) for t in token_counts}):
+            room = min(self.max_model_len - 2, self.cache.num_pages * self.cache.page_size - 2,
+                       self.sched_config.max_num_batched_tokens)
+            if n < 2 or n > sg.max_tokens or n > room or (n in sg.graphs and sg.graphs[n].captured):
+                continue
+            self.generate([[0] * n], temperature=0.0, max_new_tokens=1, ignore_eos=True)
+            if n in sg.graphs and sg.graphs[n].captured:
+                done.append(n)
+        return done
+
     # -- generation ---------------------------------------------------------------------
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                  sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None, *,

@@ -74,3 +74,28 @@ def test_a_step_longer_than_the_limit_is_launched(tmp_path):
     # without the device-resident block tables there is nothing to capture against
     plain = make_runner(model, page_size=page, num_pages=100, max_slots=4)
     assert not plain.enable_step_graphs(64)
+
+
+@pytest.mark.gpu
+def test_engine_warms_up_and_generates_the_same_tokens(tmp_path):
+    from prelude_b200 import Engine
+    cfg = tiny.PARAMS["E"][0]
+    folder = tiny.make_folder(tmp_path, "E", torch.float32)
+    prompts = [tiny.random_ids(n, cfg["vocab_size"], 11 + n) for n in (3, 40, 97, 150)]
+    outs = []
+    for graphs in (False, True):
+        engine = Engine(folder, dtype="f32", device="cuda:0", page_size=8, num_pages=120, max_running_requests=4,
+                        cuda_graph=graphs)
+        if graphs:
+            assert engine.warmup_prompt_steps([40, 100]) == [64, 128]
+            assert engine.warmup_prompt_steps([40, 100]) == []          # already there
+        else:
+            assert engine.warmup_prompt_steps([40, 100]) == []
+        one_by_one = [engine.generate(p, temperature=0.0, max_new_tokens=5, ignore_eos=True).token_ids for p in prompts]
+        together = [r.token_ids for r in engine.generate(prompts, temperature=0.0, max_new_tokens=5, ignore_eos=True)]
+        assert one_by_one == together
+        outs.append(together)
+        if graphs:
+            assert engine.runner.graph_steps_run >= 4
+        engine.cache.check()
+    assert outs[0] == outs[1]                  # 32-bit: the same kernels on every row, captured or launched
