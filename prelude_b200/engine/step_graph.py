@@ -62,6 +62,17 @@ class _Recorder:
         self._graph.replay()                              # a capture runs nothing: what follows needs the piece's results
         self._graph = None
 
+    def abandon(self) -> None:
+        """A launch failed while a piece was being captured: close the capture and drop what was recorded."""
+        if self.capturing and self._graph is not None:
+            try:
+                self._graph.capture_end()
+            except Exception:
+                pass
+        self.capturing, self._graph = False, None
+        self.pieces.clear()
+        self.between.clear()
+
     def run_between_pieces(self, fn: Callable[[], None]) -> None:
         self.end_piece()
         fn()
@@ -91,6 +102,7 @@ class StepGraph:
         self.recorder = _Recorder(pool, stream)
         self.delta = self.res = None
         self.captured = False
+        self.failed = False                 # a capture that raised: the bucket's steps are launched from then on
         self.replays = 0
 
     # -- the step's inputs --------------------------------------------------------------
@@ -146,9 +158,14 @@ class StepGraph:
             if not self.captured:
                 rec = self.recorder
                 self.batch.extras["recorder"] = rec
-                rec.begin_piece()
-                self.delta, self.res = model.forward_hidden(self.batch, caches)
-                rec.end_piece()
+                try:
+                    rec.begin_piece()
+                    self.delta, self.res = model.forward_hidden(self.batch, caches)
+                    rec.end_piece()
+                except BaseException:
+                    rec.abandon()                          # never leave the stream capturing
+                    self.failed = True
+                    raise
                 self.captured = True
             else:
                 for i, piece in enumerate(self.recorder.pieces):
@@ -178,8 +195,9 @@ class StepGraphs:
 
     def usable(self, n_tokens: int, n_requests: int, longest: int) -> bool:
         cache = self.runner.cache
+        g = self.graphs.get(bucket_of(n_tokens))
         return (bool(cache.device_tables) and bucket_of(n_tokens) <= self.max_tokens and n_requests <= cache.max_slots
-                and longest <= cache.table_width * cache.page_size)
+                and longest <= cache.table_width * cache.page_size and not (g is not None and g.failed))
 
     def get(self, n_tokens: int) -> StepGraph:
         b = bucket_of(n_tokens)

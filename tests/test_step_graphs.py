@@ -99,3 +99,36 @@ def test_engine_warms_up_and_generates_the_same_tokens(tmp_path):
             assert engine.runner.graph_steps_run >= 4
         engine.cache.check()
     assert outs[0] == outs[1]                  # 32-bit: the same kernels on every row, captured or launched
+
+
+@pytest.mark.gpu
+def test_a_recording_that_fails_leaves_no_capture_open(tmp_path, monkeypatch):
+    cfg, _, page = tiny.PARAMS["E"]
+    folder = tiny.make_folder(tmp_path, "E", torch.bfloat16)
+    from prelude_b200.engine.loading import load_model, make_runner
+    from prelude_b200.engine.runner import StepEntry
+    from prelude_b200.parts import mlp
+    model = load_model(folder, torch.bfloat16, "cuda:0")
+    runner = make_runner(model, page_size=page, num_pages=100, max_slots=4, max_request_tokens=400)
+    assert runner.enable_step_graphs(128)
+    toks = tiny.random_ids(60, cfg["vocab_size"], 5)
+    real = mlp.GatedMlp.forward
+    calls = []
+
+    def failing(self, x):
+        calls.append(1)
+        if len(calls) == 2:                                   # in the second layer, in the middle of a piece
+            raise RuntimeError("made to fail")
+        return real(self, x)
+    monkeypatch.setattr(mlp.GatedMlp, "forward", failing)
+    with pytest.raises(RuntimeError, match="made to fail"):
+        runner.step([StepEntry("a", toks[:40], [39])])
+    assert not torch.cuda.is_current_stream_capturing()
+    monkeypatch.setattr(mlp.GatedMlp, "forward", real)
+    runner.finish("a")
+    want = runner.step([StepEntry("b", toks[:40], [39])])     # the bucket is launched kernel by kernel from now on
+    assert runner.graph_steps_run == 0 and runner.step_graphs.graphs[64].failed
+    runner.finish("b")
+    other = make_runner(model, page_size=page, num_pages=100, max_slots=4)
+    got = other.step([StepEntry("b", toks[:40], [39])])
+    assert torch.equal(want, got)
