@@ -81,11 +81,9 @@ def _ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
-def build_step_batch(items: Sequence[StepItem], block_tables: Dict[int, List[List[int]]],
-                     state_slots: Sequence[int], device: torch.device, vocab_size: int,
-                     max_positions: int, min_table_width: int = 1) -> StepBatch:
-    """Pack ``items``; ``block_tables[group][i]`` is the page list of item i in
-    that cache group (-1 for a page that a window has passed)."""
+def pack_items(items: Sequence[StepItem], vocab_size: int, max_positions: int):
+    """The host arrays of a step, checked: (q_lens [R], q_start [R], kv_len [R], cu_q [R + 1], tokens [T] int64,
+    positions [T], logit_rows [W]), the requests' tokens packed one after the other."""
     R = len(items)
     if R == 0:
         raise ValueError("a step needs at least one request")
@@ -102,7 +100,6 @@ def build_step_batch(items: Sequence[StepItem], block_tables: Dict[int, List[Lis
     tokens = np.concatenate([np.asarray(it.tokens, dtype=np.int64) for it in items])
     if tokens.min() < 0 or tokens.max() >= vocab_size:
         raise ValueError(f"token ids must lie in [0, {vocab_size})")
-    token_seq = np.repeat(np.arange(R, dtype=np.int32), q_lens)
     positions = (np.arange(T, dtype=np.int32) - np.repeat(cu_q[:-1], q_lens)) + np.repeat(q_start, q_lens)
     rows = []
     for i, it in enumerate(items):
@@ -110,7 +107,18 @@ def build_step_batch(items: Sequence[StepItem], block_tables: Dict[int, List[Lis
             if not 0 <= wi < q_lens[i]:
                 raise ValueError(f"request {it.request_id!r}: wanted place {wi} outside its {q_lens[i]} tokens")
             rows.append(int(cu_q[i]) + int(wi))
-    logit_rows = np.asarray(rows, dtype=np.int32)
+    return q_lens, q_start, kv_len, cu_q, tokens, positions.astype(np.int32), np.asarray(rows, dtype=np.int32)
+
+
+def build_step_batch(items: Sequence[StepItem], block_tables: Dict[int, List[List[int]]],
+                     state_slots: Sequence[int], device: torch.device, vocab_size: int,
+                     max_positions: int, min_table_width: int = 1) -> StepBatch:
+    """Pack ``items``; ``block_tables[group][i]`` is the page list of item i in
+    that cache group (-1 for a page that a window has passed)."""
+    R = len(items)
+    q_lens, q_start, kv_len, cu_q, tokens, positions, logit_rows = pack_items(items, vocab_size, max_positions)
+    T = int(cu_q[-1])
+    token_seq = np.repeat(np.arange(R, dtype=np.int32), q_lens)
     slots = np.asarray(list(state_slots), dtype=np.int32)
     if slots.shape[0] != R:
         raise ValueError("one state slot per request")

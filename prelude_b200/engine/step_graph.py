@@ -31,7 +31,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from .batch import StepBatch, StepItem
+from .batch import StepBatch, StepItem, pack_items
 
 
 def bucket_of(n_tokens: int) -> int:
@@ -109,29 +109,12 @@ class StepGraph:
     def load(self, items: Sequence[StepItem], slots: Sequence[int], vocab_size: int, max_positions: int) -> None:
         b, o, h = self.batch, self.offsets, self.host.numpy()
         R = len(items)
-        q_lens = np.array([len(it.tokens) for it in items], dtype=np.int32)
-        if (q_lens <= 0).any():
-            raise ValueError("every request of a step brings at least one token")
-        T = int(q_lens.sum())
-        q_start = np.array([it.position_start for it in items], dtype=np.int32)
-        kv_len = q_start + q_lens
-        if (q_start < 0).any() or int(kv_len.max()) > max_positions:
-            raise ValueError(f"positions must lie in [0, {max_positions}); a request would reach {int(kv_len.max())}")
-        tokens = np.concatenate([np.asarray(it.tokens, dtype=np.int64) for it in items])
-        if tokens.min() < 0 or tokens.max() >= vocab_size:
-            raise ValueError(f"token ids must lie in [0, {vocab_size})")
-        cu_q = np.zeros(R + 1, dtype=np.int32)
-        np.cumsum(q_lens, out=cu_q[1:])
+        q_lens, q_start, kv_len, cu_q, tokens, positions, rows = pack_items(items, vocab_size, max_positions)
+        T = int(cu_q[-1])
         slots = np.asarray(list(slots), dtype=np.int32)
-        rows = []
-        for i, it in enumerate(items):
-            for wi in it.want:
-                if not 0 <= wi < q_lens[i]:
-                    raise ValueError(f"request {it.request_id!r}: wanted place {wi} outside its {q_lens[i]} tokens")
-                rows.append(int(cu_q[i]) + int(wi))
         h[:] = 0
         h[o[0]:o[0] + T] = tokens
-        h[o[1]:o[1] + T] = (np.arange(T, dtype=np.int32) - np.repeat(cu_q[:-1], q_lens)) + np.repeat(q_start, q_lens)
+        h[o[1]:o[1] + T] = positions
         h[o[2]:o[3]] = -1                                  # padding rows belong to no request
         h[o[2]:o[2] + T] = np.repeat(slots, q_lens)        # a token's row of the device-resident block table
         h[o[3]:o[3] + R + 1] = cu_q
