@@ -27,6 +27,7 @@ import torch
 
 from ..ops import kernels as K
 from .batch import StepBatch
+from .capture import no_collection
 
 
 class DecodeGraph:
@@ -91,7 +92,7 @@ class DecodeGraph:
         self.dev_samp.copy_(saved_samp)
         before = library.launch_count
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with no_collection(), torch.cuda.graph(graph):
             self._body()
         self.launches = library.launch_count - before
         self.graph = graph

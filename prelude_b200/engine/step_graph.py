@@ -32,6 +32,7 @@ import numpy as np
 import torch
 
 from .batch import StepBatch, StepItem, pack_items
+from .capture import no_collection
 
 
 def bucket_of(n_tokens: int) -> int:
@@ -142,9 +143,10 @@ class StepGraph:
                 rec = self.recorder
                 self.batch.extras["recorder"] = rec
                 try:
-                    rec.begin_piece()
-                    self.delta, self.res = model.forward_hidden(self.batch, caches)
-                    rec.end_piece()
+                    with no_collection():
+                        rec.begin_piece()
+                        self.delta, self.res = model.forward_hidden(self.batch, caches)
+                        rec.end_piece()
                 except BaseException:
                     rec.abandon()                          # never leave the stream capturing
                     self.failed = True

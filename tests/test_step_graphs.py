@@ -132,3 +132,35 @@ def test_a_recording_that_fails_leaves_no_capture_open(tmp_path, monkeypatch):
     other = make_runner(model, page_size=page, num_pages=100, max_slots=4)
     got = other.step([StepEntry("b", toks[:40], [39])])
     assert torch.equal(want, got)
+
+
+@pytest.mark.gpu
+def test_graphs_of_a_dropped_engine_are_not_collected_inside_a_capture(tmp_path):
+    # An engine that is no longer used leaves its captured graphs in reference cycles.  The cycle collector must
+    # not free them while another engine records: destroying a graph during a capture invalidates the capture.
+    # With the collector's threshold at its lowest it would run at almost every allocation of the recording.
+    import gc
+    from prelude_b200 import Engine
+    cfg = tiny.PARAMS["E"][0]
+    folder = tiny.make_folder(tmp_path, "E", torch.bfloat16)
+    prompts = [tiny.random_ids(n, cfg["vocab_size"], 5 + n) for n in (40, 70)]
+
+    def run():
+        engine = Engine(folder, dtype="bf16", device="cuda:0", page_size=16, num_pages=64, max_running_requests=4)
+        out = [r.token_ids for r in engine.generate(prompts, temperature=0.0, max_new_tokens=6, ignore_eos=True)]
+        assert engine.runner.graph_steps_run >= 1
+        holder = {"engine": engine}
+        holder["self"] = holder                  # a cycle: only the collector frees this engine and its graphs
+        return out
+
+    old = gc.get_threshold()
+    gc.disable()                                 # the garbage of the first run stays until a collection is asked for
+    try:
+        first = run()
+        gc.enable()
+        gc.set_threshold(1, 1, 1)
+        second = run()
+    finally:
+        gc.set_threshold(*old)
+        gc.enable()
+    assert first == second
