@@ -119,3 +119,24 @@ def test_bf16_with_every_product_on_the_tcgen05_kernel(folders, monkeypatch, whi
     runner = _runner(folder, torch.bfloat16, page, harness.peak_tokens(schedule, page) // page)
     _compare(harness.run_schedule(runner, schedule), ref, torch.bfloat16)
     assert int(linear.tc_status(torch.device("cuda:0")).item()) == 0
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("cut", ["tail_decode", "mixed"])
+def test_bf16_with_the_feed_forward_of_small_steps_in_one_launch(folders, monkeypatch, which, cut):
+    """The same comparison with the feed-forward of every step of up to 16 tokens on the chain kernel (off by
+    default): single decoded tokens, short portions, and the steps that mix them."""
+    from prelude_b200.ops import linear
+    from prelude_b200.parts import mlp
+    monkeypatch.setattr(mlp, "MLP_CHAIN", True)
+    calls = []
+    chain = mlp.gated_mlp_chain
+    monkeypatch.setattr(mlp, "gated_mlp_chain", lambda *a: calls.append(1) or chain(*a))
+    folder = folders[(which, torch.bfloat16)]
+    reqs = _requests(which)
+    ref = _reference(which, folder, reqs)
+    page = tiny.PARAMS[which][2]
+    schedule = {"tail_decode": harness.tail_decode, "mixed": harness.mixed}[cut](reqs)
+    runner = _runner(folder, torch.bfloat16, page, harness.peak_tokens(schedule, page) // page)
+    _compare(harness.run_schedule(runner, schedule), ref, torch.bfloat16)
+    assert len(calls) > 0 and int(linear.tc_status(torch.device("cuda:0")).item()) == 0
