@@ -19,6 +19,11 @@ prints one JSON line:
 
 Every decode step reads the whole model (8 GB at full size), far more than the
 126 MB L2, so no flush is needed between steps ("l2": "inputs_exceed_l2").
+
+``--workload serving`` measures something else and prints a line of its own: a
+mixed continuous batch through Engine.generate() (BASELINE.json configs[3]: 32
+requests, prompts of 128 to 2,048 tokens cut into portions of 512 beside the
+running decodes, 256 tokens each), as generated tokens a second by the wall clock.
 """
 import argparse
 import json
@@ -108,7 +113,7 @@ class ClockSampler:
 MODEL = QWEN3_4B            # what --model-size chose
 
 
-def build_engine(layers, max_running, num_pages):
+def build_engine(layers, max_running, num_pages, prefill_chunk=0):
     import torch
     from prelude_b200 import Engine
     from prelude_b200.config import load_model_config
@@ -121,7 +126,8 @@ def build_engine(layers, max_running, num_pages):
     del tensors
     torch.cuda.empty_cache()
     return Engine(model, page_size=PAGE_SIZE, num_pages=num_pages, max_running_requests=max_running,
-                  max_num_batched_tokens=max(8192, PREFILL_TOKENS), max_model_len=CONTEXT_LEN, cuda_graph=True, cuda_graph_max_bs=64), cfg
+                  max_num_batched_tokens=max(8192, PREFILL_TOKENS), long_prefill_token_threshold=prefill_chunk,
+                  max_model_len=CONTEXT_LEN, cuda_graph=True, cuda_graph_max_bs=64), cfg
 
 
 def weight_bytes_per_step(cfg):
@@ -237,6 +243,53 @@ def time_e2e(engine, cfg, batch, steps):
             "d2h_bytes_per_step": gr.d2h_bytes, "decode_ms": decode_ms}, (t0, t1)
 
 
+def serve(args):
+    """A mixed continuous batch through ``Engine.generate`` (host tokens in, host tokens out): ``--requests`` prompts
+    of uniform random ids with lengths uniform in [128, 2048], prompts cut into portions of ``--prefill-chunk``
+    tokens beside the running decodes, ``--new-tokens`` greedy tokens each.  One JSON line of its own."""
+    import copy
+    import random
+    import time
+    import torch
+    rng = random.Random(7)
+    lens = [rng.randint(128, 2048) for _ in range(args.requests)]
+    pages = sum(-(-(n + args.new_tokens + 1) // PAGE_SIZE) for n in lens) + 64
+    engine, cfg = build_engine(args.layers, args.requests, pages, prefill_chunk=args.prefill_chunk)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    engine.warmup(range(1, args.requests + 1))
+    engine.warmup_prompt_steps([args.prefill_chunk])
+    engine.generate(prompts[:2], temperature=0.0, max_new_tokens=4, ignore_eos=True)
+    before = copy.copy(engine.stats())
+    torch.cuda.synchronize()
+    clocks = ClockSampler()
+    clocks.start()
+    t0 = time.time()
+    results = engine.generate(prompts, temperature=0.0, max_new_tokens=args.new_tokens, ignore_eos=True)
+    torch.cuda.synchronize()
+    t1 = time.time()
+    clocks.stop()
+    st = engine.stats()
+    out_tokens = sum(r.completion_tokens for r in results)
+    ttft = sorted(r.ttft_ms for r in results)
+    line = {
+        "metric": f"serving: {args.requests} requests, prompts of 128 to 2,048 tokens in portions of {args.prefill_chunk}, "
+                  f"{args.new_tokens} greedy tokens each (Qwen3-{args.model_size.upper()} sizes, random weights, bf16)",
+        "value": round(out_tokens / (t1 - t0), 1), "unit": "generated tok/s", "n_gpus": 1, "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours", "seconds": round(t1 - t0, 3),
+        "prompt_tokens": sum(lens), "generated_tokens": out_tokens,
+        "total_tok_s": round((sum(lens) + out_tokens) / (t1 - t0), 1),
+        "ttft_ms": {"p50": round(statistics.median(ttft), 1), "p95": round(ttft[int(0.95 * (len(ttft) - 1))], 1), "max": round(ttft[-1], 1)},
+        "steps": st.steps - before.steps, "decode_steps": st.decode_steps - before.decode_steps,
+        "captured_steps": st.graph_steps - before.graph_steps, "preemptions": st.preemptions - before.preemptions,
+        "config": {"model": f"qwen3-{args.model_size}-sizes", "layers": args.layers, "layers_full": MODEL["num_hidden_layers"],
+                   "requests": args.requests, "prefill_chunk": args.prefill_chunk, "new_tokens": args.new_tokens, "page_size": PAGE_SIZE},
+        "clocks": clocks.summary([(t0, t1)]),
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     global MODEL, PREFIX_LEN, CONTEXT_LEN, PAGE_SIZE, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
@@ -252,6 +305,11 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt (the contract's is 2,048)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own)")
+    ap.add_argument("--requests", type=int, default=32, help="serving: number of requests")
+    ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: tokens per portion of a prompt")
+    ap.add_argument("--new-tokens", type=int, default=256, help="serving: generated tokens per request")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -269,6 +327,9 @@ def main():
     PREFILL_TOKENS = args.prefill_tokens
     CONTEXT_LEN = max(CONTEXT_LEN, PREFIX_LEN + args.steps + args.warmup + 64, PREFILL_TOKENS + 64)
     args.layers = args.layers or MODEL["num_hidden_layers"]
+    if args.workload == "serving":
+        CONTEXT_LEN = max(CONTEXT_LEN, 2048 + args.new_tokens + 64)
+        return serve(args)
     import torch
     pk = peaks()
     # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages
