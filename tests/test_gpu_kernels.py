@@ -111,13 +111,22 @@ def test_gemm_stream_partial_sums(M, N, K_, splits):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("T,I", [(1, 8), (13, 9728), (6, 200), (3, 37)])
+@pytest.mark.parametrize("T,I", [(1, 8), (13, 9728), (6, 200), (3, 37), (2050, 1216), (5, 48)])
 def test_silu_mul(dtype, T, I):
     gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)
     g, u = gu.float()[:, :I], gu.float()[:, I:]
     want = g / (1 + torch.exp(-g)) * u
     got = K().silu_mul(gu)
     assert (got.float() - want).abs().max() <= tol(dtype, float(want.abs().max()))
+    # gates far out on both sides: silu(g) -> 0 and -> g, never a NaN or an infinity
+    far = torch.tensor([-300.0, -100.0, -88.0, -20.0, 0.0, 20.0, 88.0, 300.0], device=DEV)[:I]
+    gu2 = gu.clone()
+    gu2[0, :far.numel()] = far.to(dtype)
+    gu2[0, I:I + far.numel()] = 2.0
+    got2 = K().silu_mul(gu2).float()
+    g2 = gu2.float()[0, :far.numel()]
+    want2 = g2 / (1 + torch.exp(-g2)) * 2.0
+    assert torch.isfinite(got2).all() and (got2[0, :far.numel()] - want2).abs().max() <= tol(dtype, 600.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
