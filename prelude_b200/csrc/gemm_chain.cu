@@ -33,6 +33,8 @@
 #define GC_CHAINS 4                             // independent accumulators per warp
 #define GC_SMEM_LIMIT (227 * 1024 - 2048)
 #define GC_MAX_PHASES 4
+#define GC_MAX_GROUPS 16                        // groups of blocks at one barrier
+#define GC_COUNTERS (GC_MAX_PHASES * GC_MAX_GROUPS + 1)
 
 struct GcPhase {
     const __nv_bfloat16* W;     // [N, ldw] (gated: N gate rows, then N up rows)
@@ -46,6 +48,7 @@ struct GcPhase {
     int ks, n_chunks;           // elements of K per stage, chunks per row of a part
     int gated;                  // the output is silu(gate) * up
     int kind;                   // 0: bfloat16 result; 1: float32 partial sums, one set per part of K
+    int groups;                 // the barrier before this phase: groups of blocks that wait for one another only
 };
 
 struct GcParams {
@@ -55,7 +58,7 @@ struct GcParams {
     int stages;                 // stages of the ring
     int slot_bytes;             // bytes of one stage
     int x_bytes;                // bytes kept for x (the largest phase's)
-    unsigned* gbar;             // [2] zero on entry and on exit: arrivals at the barriers, blocks that have left
+    unsigned* gbar;             // [GC_COUNTERS] zero on entry and on exit: arrivals per (barrier, group), blocks that have left
     int* status;
 };
 
@@ -172,21 +175,25 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         if (q == 0) {
             pb_grid_dep_wait();                                // x of the first phase comes from the kernel before
         } else {
-            // every block has written its share of the phase before: this thread's stores are made visible, the
-            // block's threads meet, one of them counts the block in and waits for the others
-            __threadfence();
+            // every block has written its share of the phase before.  The block's threads meet; one of them makes
+            // their stores visible to the device (a fence after the meeting covers them all), counts the block in
+            // and waits for the others.  Where the blocks that produce a part of x are the ones that consume it
+            // (f.groups > 1), a block waits for its own group only.
             gc_bar_compute();
             if (threadIdx.x == 0) {
-                atomicAdd(p.gbar, 1u);
-                const unsigned target = gridDim.x * (unsigned)q;
+                const unsigned per_group = gridDim.x / (unsigned)f.groups;
+                unsigned* counter = p.gbar + (q - 1) * GC_MAX_GROUPS + blockIdx.x / per_group;
+                __threadfence();
+                atomicAdd(counter, 1u);
                 const long long t0 = clock64();
-                while (gc_ld_acquire(p.gbar) < target) {
+                while (gc_ld_acquire(counter) < per_group) {
                     if (clock64() - t0 > (1ll << 31)) {        // about a second: some block is not running
                         *(volatile int*)&s_dead = 1;
                         if (p.status) atomicExch(p.status, 13);
                         break;
                     }
                 }
+                __threadfence();
             }
             gc_bar_compute();
         }
@@ -332,9 +339,8 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     // the block that leaves last puts the counters back to zero for the next launch
     if (p.n_phases > 1 && threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(p.gbar + 1, 1u) == gridDim.x - 1) {
-            p.gbar[0] = 0;
-            p.gbar[1] = 0;
+        if (atomicAdd(p.gbar + GC_COUNTERS - 1, 1u) == gridDim.x - 1) {
+            for (int i = 0; i < GC_COUNTERS; ++i) p.gbar[i] = 0;
         }
     }
 }
@@ -409,6 +415,18 @@ static int gc_launch(GcParams& p, cudaStream_t stream) {
         int bx = grid / f.splits;
         if (bx > (f.N + 7) / 8) bx = (f.N + 7) / 8;           // at least 8 features per block
         f.blocks_x = bx < 1 ? 1 : bx;
+        // The barrier before this phase.  When the phase before gave every block of the grid a run of its features,
+        // this one cuts K into parts that are whole runs of those blocks, and every block works in both, then part g
+        // of x is written by blocks [g * grid / splits, (g + 1) * grid / splits) and read by the same blocks
+        // (block b works on part b / blocks_x): they wait for one another only.
+        f.groups = 1;
+        if (q > 0) {
+            const GcPhase& a = p.ph[q - 1];
+            // (the first block of group g starts at feature g * (grid / splits) * N / grid = g * K exactly)
+            if (a.splits == 1 && a.blocks_x == grid && f.blocks_x * f.splits == grid && f.splits <= GC_MAX_GROUPS &&
+                a.N == f.K * f.splits)
+                f.groups = f.splits;
+        }
     }
     PB_REQUIRE(p.n_phases == 1 || p.gbar != nullptr, "gemm_chain: more than one phase needs the barrier's counters");
     size_t smem = 0;
@@ -439,6 +457,9 @@ static void gc_mlp_phases(GcParams& p, const void* X, long long ldx, const void*
     b.out = parts; b.ldo = H; b.split_stride = (long long)M * H; b.N = H; b.K = I / splits; b.splits = splits; b.gated = 0; b.kind = 1;
 }
 
+// 32-bit counters that a chain's barriers need: zero before the first launch, left zero by every launch.
+PB_API int pb_mlp_chain_counters() { return GC_COUNTERS; }
+
 // Whether the chain takes a gated feed-forward of these sizes (else the caller launches the products one by one).
 PB_API int pb_mlp_chain_supported(int M, int H, int I, int splits, long long ldx, long long ldw1, long long ldw2) {
     if (M < 1 || M > 16 || H < 16 || H % 16 || I < 16 || splits < 1 || I % (16 * splits) || ldx % 8 || ldw1 % 8 || ldw2 % 8) return 0;
@@ -451,8 +472,8 @@ PB_API int pb_mlp_chain_supported(int M, int H, int I, int splits, long long ldx
 // A gated feed-forward for the few rows of a decode step in one launch:
 //   act   [M, I] bfloat16 = silu(x Wg^T) * (x Wu^T)   with W_gate_up [2 I, ldw1] (I gate rows, then I up rows)
 //   parts [splits][M, H] float32: part s = act[:, s-th part of I] W_down[:, s-th part of I]^T; their sum is the result.
-// act is scratch that the caller provides.  gbar: two zeroed 32-bit counters, left zeroed; calls that overlap on
-// the device need counters of their own.
+// act is scratch that the caller provides.  gbar: zeroed 32-bit counters, left zeroed; calls that overlap on
+// the device need counters of their own.  (pb_mlp_chain_counters() of them.)
 PB_API int pb_mlp_chain_bf16(const void* X, long long ldx, const void* W_gate_up, long long ldw1, const void* W_down,
                              long long ldw2, void* act, float* parts, int M, int H, int I, int splits, unsigned* gbar,
                              int* status, cudaStream_t stream) {

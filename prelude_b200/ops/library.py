@@ -48,6 +48,7 @@ _SIGNATURES = {
     "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P], I),
     "pb_gemm_stream_supported": ([I, I, I, L, L], I),
     "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, I, P, P], I),
+    "pb_mlp_chain_counters": ([], I),
     "pb_mlp_chain_supported": ([I, I, I, I, L, L, L], I),
     "pb_mlp_chain_bf16": ([P, L, P, L, P, L, P, P, I, I, I, I, P, P, P], I),
     "pb_gemm_tc_supported": ([I, I, I, L, L], I),

@@ -87,11 +87,11 @@ _chain_counters: Dict[torch.device, torch.Tensor] = {}
 
 
 def _chain_counters_for(device: torch.device) -> torch.Tensor:
-    """The two counters of the chain kernel's barrier: zero before the first launch, and every launch leaves them
-    zero.  Launches on one stream follow one another, so they share the pair."""
+    """The counters of the chain kernel's barriers: zero before the first launch, and every launch leaves them
+    zero.  Launches on one stream follow one another, so they share them."""
     c = _chain_counters.get(device)
     if c is None:
-        c = _chain_counters[device] = torch.zeros(2, dtype=torch.int32, device=device)
+        c = _chain_counters[device] = torch.zeros(_l.library().pb_mlp_chain_counters(), dtype=torch.int32, device=device)
     return c
 
 
