@@ -140,3 +140,31 @@ def test_bf16_with_the_feed_forward_of_small_steps_in_one_launch(folders, monkey
     runner = _runner(folder, torch.bfloat16, page, harness.peak_tokens(schedule, page) // page)
     _compare(harness.run_schedule(runner, schedule), ref, torch.bfloat16)
     assert len(calls) > 0 and int(linear.tc_status(torch.device("cuda:0")).item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which", ["A", "C", "E"])
+def test_the_first_tokens_of_a_sequence(folders, which, dtype):
+    """A request fed token by token from an empty cache: the step at position 0 attends to one key, its own; the
+    page table has one page, then a second when the first is full; and a second request starts in between, so
+    that the first tokens of one sequence lie beside later tokens of another in the same step."""
+    folder = folders[(which, dtype)]
+    cfg, _, page = tiny.PARAMS[which]
+    n = 2 * page + 3                                         # past the first page's edge and the second's
+    reqs = {"p": tiny.random_ids(n, cfg["vocab_size"], 5), "q": tiny.random_ids(page + 2, cfg["vocab_size"], 6)}
+    ref = _reference(which, folder, reqs)
+    late = page - 1                                          # q's first token arrives beside p's last token of its first page
+    schedule = []
+    for i in range(n):
+        entries = [("p", [reqs["p"][i]], [0])]
+        j = i - late
+        if 0 <= j < len(reqs["q"]):
+            entries.append(("q", [reqs["q"][j]], [0]))
+        schedule.append((entries, ["q"] if j == len(reqs["q"]) - 1 else []))
+    schedule[-1] = (schedule[-1][0], schedule[-1][1] + ["p"])
+    runner = _runner(folder, dtype, page, harness.peak_tokens(schedule, page) // page)
+    got = harness.run_schedule(runner, schedule)
+    assert len(got) == n + len(reqs["q"]) and ("p", 0) in got and ("q", 0) in got
+    _compare(got, ref, dtype)
+    runner.cache.check()
+    assert runner.cache.used_pages() == 0
