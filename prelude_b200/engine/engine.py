@@ -229,27 +229,36 @@ class Engine:
             sched.add_request(rid, prompt, p, self.max_model_len)
             ids.append(rid)
         done: Dict[object, GenerateResult] = {}
-        while sched.has_work():
-            items = sched.schedule()
-            self._collect(sched, done, first_token_at, t0)
-            if not items:
-                if sched.has_work():
-                    raise RuntimeError("the scheduler has work but could schedule nothing")
-                break
-            burst = self._burst_length(sched, items)
-            if burst >= 2:
-                for j, tokens in enumerate(self._run_burst(items, burst)):
-                    for it, tok in zip(items, tokens):
-                        sched.on_step_done(it if j == 0 else ScheduledItem(it.seq, 1, it.start + j), tok, self.eos_token_ids)
+        try:
+            while sched.has_work():
+                items = sched.schedule()
                 self._collect(sched, done, first_token_at, t0)
-                continue
-            tokens = self._run_step(items)
-            now = time.perf_counter()
-            for it, tok in zip(items, tokens):
-                if tok is not None and it.seq.request_id not in first_token_at:
-                    first_token_at[it.seq.request_id] = now
-                sched.on_step_done(it, tok, self.eos_token_ids)
-            self._collect(sched, done, first_token_at, t0)
+                if not items:
+                    if sched.has_work():
+                        raise RuntimeError("the scheduler has work but could schedule nothing")
+                    break
+                burst = self._burst_length(sched, items)
+                if burst >= 2:
+                    for j, tokens in enumerate(self._run_burst(items, burst)):
+                        for it, tok in zip(items, tokens):
+                            sched.on_step_done(it if j == 0 else ScheduledItem(it.seq, 1, it.start + j), tok, self.eos_token_ids)
+                    self._collect(sched, done, first_token_at, t0)
+                    continue
+                tokens = self._run_step(items)
+                now = time.perf_counter()
+                for it, tok in zip(items, tokens):
+                    if tok is not None and it.seq.request_id not in first_token_at:
+                        first_token_at[it.seq.request_id] = now
+                    sched.on_step_done(it, tok, self.eos_token_ids)
+                self._collect(sched, done, first_token_at, t0)
+        except BaseException:
+            # a step failed (a kernel's status word, an interrupt, ...): what the unfinished requests hold goes back,
+            # so that the engine can be used again
+            for rid in ids:
+                if rid not in done:
+                    sched.abort(rid)
+            sched.drain_finished()
+            raise
         self._stats.preemptions += sched.stats["preemptions"]
         return [done[r] for r in ids]
 

@@ -180,3 +180,27 @@ def test_command_line(folders):
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "prelude"), "--model", folders["A"], "--device", "cpu",
                           "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
     assert bad.returncode != 0 and "no cpu path" in bad.stderr
+
+
+def test_a_generation_that_fails_gives_its_pages_back(folders, monkeypatch):
+    # a step that raises in the middle of a generation: the call raises, nothing stays held, the engine goes on
+    cfg, w = tiny.PARAMS["A"][0], tiny.read_weights(folders["A"])
+    eng = _engine(folders["A"], cuda_graph=False)
+    prompts = _prompts("A", [9, 17, 5])
+    step, calls = eng.runner.step, []
+
+    def failing(entries, **kw):
+        calls.append(len(entries))
+        if len(calls) == 3:
+            raise RuntimeError("made to fail")
+        return step(entries, **kw)
+
+    monkeypatch.setattr(eng.runner, "step", failing)
+    with pytest.raises(RuntimeError, match="made to fail"):
+        eng.generate(prompts, temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    assert len(calls) == 3
+    eng.cache.check()
+    assert eng.cache.used_pages() == 0 and not eng.cache.requests
+    monkeypatch.setattr(eng.runner, "step", step)
+    got = eng.generate(prompts, temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    assert [r.token_ids for r in got] == [greedy_generate(cfg, w, p, 6) for p in prompts]
