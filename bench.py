@@ -59,10 +59,13 @@ def peaks():
             raw = json.load(f)
         out = dict(FALLBACK_PEAKS, source="measured")
         for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
-            if isinstance(raw.get(k), (int, float)) and raw[k] > 0:
-                out[k] = float(raw[k])
+            v = raw.get(k)
+            if isinstance(v, dict):                          # a record around the figure
+                v = v.get("value")
+            if isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+                out[k] = float(v)
         return out
-    except (OSError, ValueError):
+    except (OSError, ValueError, AttributeError):
         return dict(FALLBACK_PEAKS)
 
 
