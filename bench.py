@@ -139,7 +139,7 @@ def weight_bytes_per_step(cfg):
     H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
     qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
     per_layer = 2 * (qkv * H + H * cfg["num_attention_heads"] * cfg["head_dim"] + 3 * I * H) + 4 * (2 * H + 2 * cfg["head_dim"])
-    head = 2 * cfg["vocab_size"] * H * (1 if cfg["tie_word_embeddings"] else 1)
+    head = 2 * cfg["vocab_size"] * H          # tied or not: the head once; a separate table only at the step's token rows
     return L * per_layer + head + 4 * H
 
 
