@@ -40,15 +40,12 @@ def sampling_mode(temperature: float, top_k, top_p: float) -> str:
 
 def filter_top_p(probs: np.ndarray, top_p: float) -> np.ndarray:
     """Sort descending, keep tokens until the running sum reaches top_p, zero the rest
-    (logits_processor.rs:51-63)."""
+    (logits_processor.rs:51-63): a token stays if the sum of those before it, in that order, is below top_p."""
     order = np.argsort(-probs, kind="stable")
+    sorted_probs = probs[order].astype(np.float64)
+    before = np.cumsum(sorted_probs) - sorted_probs
     out = probs.copy()
-    cum = 0.0
-    for idx in order:
-        if cum >= top_p:
-            out[idx] = 0.0
-        else:
-            cum += float(probs[idx])
+    out[order[before >= top_p]] = 0.0
     return out
 
 
