@@ -95,13 +95,16 @@ class CacheManager:
         self._fresh_slots: List[int] = []
         self.table_width = _ceil_div(max_request_tokens, page_size) if max_request_tokens else 0
         self.device_tables: Dict[int, torch.Tensor] = {}
-        self._table_updates: Dict[int, List[tuple]] = {}
+        # pending writes to the device-resident tables: group -> {cell (slot * width + index): page}.  A cell
+        # written twice before a flush keeps its last value only, so the scatter never sees an index twice.
+        self._table_updates: Dict[int, Dict[int, int]] = {}
+        if self.table_width:
+            for g in self.groups:
+                self._table_updates[g.gid] = {}
         if device is not None:
             self._allocate_tensors()
-            if self.table_width:
-                for g in self.groups:
-                    self.device_tables[g.gid] = torch.full((max_slots, self.table_width), -1, dtype=torch.int32, device=device)
-                    self._table_updates[g.gid] = []
+            for g in self.groups if self.table_width else ():
+                self.device_tables[g.gid] = torch.full((max_slots, self.table_width), -1, dtype=torch.int32, device=device)
 
     # -- device memory ----------------------------------------------------------------
     def _allocate_tensors(self) -> None:
@@ -177,9 +180,17 @@ class CacheManager:
         for gid, n in need.items():
             table = rc.tables[gid]
             new = self.groups[gid].allocator.allocate(n)
-            if gid in self._table_updates:
-                self._table_updates[gid].extend((rc.slot, len(table) + i, p) for i, p in enumerate(new))
+            for i, p in enumerate(new):
+                self._queue_table_update(gid, rc.slot, len(table) + i, p)
             table.extend(new)
+        rc.n_tokens = n_tokens
+
+    def rewind(self, rid: Hashable, n_tokens: int) -> None:
+        """The request holds fewer tokens than room was made for (a run of queued steps ended early): count
+        ``n_tokens``; the pages stay with the request, which grows into them again."""
+        rc = self.requests[rid]
+        if not 0 <= n_tokens <= rc.n_tokens:
+            raise CacheAccountingError(f"request {rid!r} holds {rc.n_tokens} tokens; cannot rewind to {n_tokens}")
         rc.n_tokens = n_tokens
 
     def trim(self, rid: Hashable) -> int:
@@ -200,28 +211,49 @@ class CacheManager:
                     g.allocator.free([table[i]])
                     table[i] = -1
                     freed += 1
-                    if g.gid in self._table_updates:
-                        self._table_updates[g.gid].append((rc.slot, i, -1))
+                    self._queue_table_update(g.gid, rc.slot, i, -1)
         return freed
 
-    def flush_table_updates(self) -> int:
-        """Bring the device-resident block tables up to date; returns the number
-        of entries written.  Rows of ended requests keep stale entries: a kernel
-        reads a row only up to its request's length, and the next owner of the
-        slot overwrites what it reads."""
+    def _queue_table_update(self, gid: int, slot: int, index: int, page: int) -> None:
+        ups = self._table_updates.get(gid)
+        if ups is not None and index < self.table_width:
+            ups[slot * self.table_width + index] = page
+
+    def _drop_table_updates(self, slot: int) -> None:
+        """Forget the pending writes to a slot's row: its request has ended or starts over, and what it queued
+        must not land in the row once another request (or its own new start) owns it."""
+        lo, hi = slot * self.table_width, (slot + 1) * self.table_width
+        for ups in self._table_updates.values():
+            for cell in [c for c in ups if lo <= c < hi]:
+                del ups[cell]
+
+    def take_table_updates(self) -> Dict[int, "object"]:
+        """group -> int32 array [2, n] (cells; pages) of the writes that are due, each cell once; the queue is
+        empty afterwards.  ``flush_table_updates`` applies them to the device-resident tables."""
         import numpy as np
-        from ..ops import kernels as K
-        total = 0
+        out = {}
         for gid, ups in self._table_updates.items():
             if not ups:
                 continue
-            arr = np.asarray([(s * self.table_width + i, p) for s, i, p in ups if i < self.table_width], dtype=np.int32)
-            self._table_updates[gid] = []
-            if arr.size == 0:
-                continue
-            dev = torch.from_numpy(np.ascontiguousarray(arr.T)).to(self.device, non_blocking=True)
+            arr = np.empty((2, len(ups)), dtype=np.int32)
+            arr[0] = np.fromiter(ups.keys(), dtype=np.int64, count=len(ups))
+            arr[1] = np.fromiter(ups.values(), dtype=np.int64, count=len(ups))
+            ups.clear()
+            out[gid] = arr
+        return out
+
+    def flush_table_updates(self) -> int:
+        """Bring the device-resident block tables up to date; returns the number
+        of entries written.  Every cell is written at most once per flush (its last
+        queued value), so the scatter's threads never race.  Rows of ended requests
+        keep stale entries: a kernel reads a row only up to its request's length,
+        and the next owner of the slot overwrites what it reads."""
+        from ..ops import kernels as K
+        total = 0
+        for gid, arr in self.take_table_updates().items():
+            dev = torch.from_numpy(arr).to(self.device, non_blocking=True)
             K.scatter_i32(self.device_tables[gid], dev[0], dev[1])
-            total += arr.shape[0]
+            total += arr.shape[1]
         return total
 
     def release(self, rid: Hashable) -> None:
@@ -232,6 +264,7 @@ class CacheManager:
         for g in self.groups:
             g.allocator.free([p for p in rc.tables[g.gid] if p >= 0])
         self.slots.free(rc.slot)
+        self._drop_table_updates(rc.slot)
         if rc.slot in self._fresh_slots:
             self._fresh_slots.remove(rc.slot)
 
@@ -243,6 +276,7 @@ class CacheManager:
             g.allocator.free([p for p in rc.tables[g.gid] if p >= 0])
             rc.tables[g.gid] = []
         rc.n_tokens = 0
+        self._drop_table_updates(rc.slot)
         if rc.slot not in self._fresh_slots:
             self._fresh_slots.append(rc.slot)
 

@@ -85,6 +85,25 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class TokenEmbeddingSpec:
+    """A table of ``vocab_size`` rows of ``hidden_size``: the residual stream starts as the rows of the step's tokens."""
+    vocab_size: int
+    hidden_size: int
+    name: str = "model.embed_tokens.weight"
+    kind: str = "token_embedding"
+
+
+@dataclass(frozen=True)
+class LinearHeadSpec:
+    """logits = x W^T over the vocabulary; ``tied`` takes the embedding's table for W."""
+    vocab_size: int
+    hidden_size: int
+    tied: bool
+    name: str = "lm_head.weight"
+    kind: str = "linear_head"
+
+
+@dataclass(frozen=True)
 class LayerCall:
     """One entry of the run order.
 
@@ -113,6 +132,19 @@ class ModelSpec:
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head.weight"
     eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
+    # The two ends of the model are parts as well.  Left at None they are the plain ones that the fields above
+    # describe (a table gather; a linear head, tied or not); an architecture with a scaled embedding, learned
+    # positions added to it, or a capped or scaled head names its own spec here.
+    embedding: Optional[object] = None
+    head: Optional[object] = None
+    # name patterns (shell style) of tensors that checkpoints of the architecture carry and the model does not read
+    ignored_tensors: Tuple[str, ...] = field(default_factory=tuple)
+
+    def embedding_spec(self) -> object:
+        return self.embedding or TokenEmbeddingSpec(self.vocab_size, self.hidden_size, self.embed_name)
+
+    def head_spec(self) -> object:
+        return self.head or LinearHeadSpec(self.vocab_size, self.hidden_size, self.tie_embeddings, self.head_name)
 
     def resolved_order(self) -> Tuple[LayerCall, ...]:
         """The run order with every ``cache`` filled in and checked."""

@@ -34,25 +34,28 @@ PB_API int pb_scatter_i32(int32_t* dst, long long dst_len, const int32_t* idx, c
 }
 
 // After a decode step: the sampled token becomes the next input, positions and
-// sampling counters move on by one.  Lets a captured step run again and again
+// sampling counters move on by one (and with them the count of tokens in the cache).  Lets a captured step run again and again
 // without the host in between.
 __global__ void decode_advance_kernel(int32_t* __restrict__ tokens, int32_t* __restrict__ positions,
-                                      long long* __restrict__ counters, const int32_t* __restrict__ sampled, int n,
-                                      int max_positions) {
+                                      int32_t* __restrict__ kv_len, long long* __restrict__ counters,
+                                      const int32_t* __restrict__ sampled, int n, int max_positions) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     tokens[i] = sampled[i];
-    if (positions[i] + 1 < max_positions) positions[i] += 1;
+    if (positions[i] + 1 < max_positions) {
+        positions[i] += 1;
+        if (kv_len) kv_len[i] = positions[i] + 1;          // tokens in the cache after the next step
+    }
     if (counters) counters[i] += 1;
 }
 
-PB_API int pb_decode_advance(int32_t* tokens, int32_t* positions, long long* counters, const int32_t* sampled, int n,
-                             int max_positions, cudaStream_t stream) {
+PB_API int pb_decode_advance(int32_t* tokens, int32_t* positions, int32_t* kv_len, long long* counters,
+                             const int32_t* sampled, int n, int max_positions, cudaStream_t stream) {
     PB_REQUIRE(n >= 0 && tokens && positions && sampled, "decode_advance: bad arguments");
     if (n == 0) return 0;
-    pb_launch(decode_advance_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, positions, counters, sampled, n, max_positions);
+    pb_launch(decode_advance_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, positions, kv_len, counters, sampled, n, max_positions);
     PB_CHECK_LAUNCH("decode_advance");
     return 0;
 }

@@ -18,6 +18,27 @@ import numpy as np
 import torch
 
 
+class StepError(RuntimeError):
+    """A kernel raised the step's status word: it met a bad page id or position, or gave up a bounded wait."""
+
+
+_STATUS = {2: "a token's page id lies outside the pool (cache write)", 3: "a position lies outside the rotation tables",
+           4: "a page id lies outside the pool (plain attention)", 5: "a block-table update points outside the table",
+           6: "a page id lies outside the pool (attention)", 7: "an attention kernel gave up waiting for a copy",
+           8: "the tensor-core product gave up waiting for a copy", 9: "a tensor-core kernel gave up waiting for its products",
+           10: "a tensor-core kernel gave up waiting for its accumulator", 11: "a streaming product's loader gave up waiting for a free stage",
+           12: "a streaming product gave up waiting for its input or weights", 13: "the chained feed-forward gave up waiting at its barrier"}
+
+
+def status_message(code: int) -> str:
+    return f"a kernel raised the step's status word: {_STATUS.get(code, 'unknown reason')} (code {code})"
+
+
+def raise_on_status(code: int) -> None:
+    if code != 0:
+        raise StepError(status_message(code))
+
+
 @dataclass
 class StepItem:
     request_id: object
@@ -50,7 +71,11 @@ class StepBatch:
     state_slots: torch.Tensor           # [R] int32
     logit_rows: torch.Tensor            # [W] int32, rows of the packed batch whose logits are wanted
     block_tables: Dict[int, torch.Tensor]   # cache group -> [R, max_blocks] int32 (-1 where no page)
-    status: torch.Tensor                # [1] int32, raised by kernels that met a bad page or position
+    status: torch.Tensor                # [1] int32, raised by kernels that met a bad page or position, or gave up a wait
+    # [T] int32, the row of ``block_tables`` that holds the pages of each token's request.  A launched step packs
+    # one table row per request, so this is ``token_seq`` itself (None); a captured step reads the
+    # device-resident tables, which have one row per state slot.  -1 marks a padding row of a captured step.
+    token_table_row: Optional[torch.Tensor] = None
     # host copies, for planning and for mixers that loop on the host
     q_lens: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int32))
     q_start_host: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int32))
@@ -61,6 +86,11 @@ class StepBatch:
     decode_only: bool = False
     extras: Dict[str, object] = field(default_factory=dict)    # per-kernel plans made once per step
     real_tokens: int = -1               # tokens that exist; a captured step is padded to n_tokens (-1: all exist)
+
+    @property
+    def table_row_of_token(self) -> torch.Tensor:
+        """What the kernels that walk block tables take for every token (see ``token_table_row``)."""
+        return self.token_seq if self.token_table_row is None else self.token_table_row
 
     @property
     def n_real(self) -> int:

@@ -14,7 +14,9 @@ outside: prompts are token ids.
 """
 from __future__ import annotations
 
+import threading
 import time
+from collections import deque
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Union
 
@@ -27,6 +29,7 @@ from ..sampling.sampler import Sampler, sampling_mode
 from .graph import DecodeGraphs
 from .loading import load_model, parse_dtype
 from ..parts.model import DecoderModel
+from .batch import raise_on_status
 from .runner import ModelRunner, StepEntry
 from .scheduler import ScheduledItem, CachePoolView, SamplingParams, Scheduler, SchedulerConfig
 
@@ -56,13 +59,23 @@ class EngineStats:
     step_ms_total: float = 0.0
 
 
-def _activation_reserve_bytes(spec, max_tokens: int, max_rows: int) -> int:
-    """A generous bound on what one step allocates beside weights and cache."""
+def _activation_reserve_bytes(model: DecoderModel, max_tokens: int, max_rows: int) -> int:
+    """A generous bound on what one step allocates beside weights and cache.  A mixer or feed-forward says what it
+    allocates per token (``activation_bytes_per_token(element size)``); one that does not say is taken to use
+    sixteen rows of the hidden width in 32-bit, so that an unknown part never counts as nothing."""
+    spec = model.spec
+    elem = 2 if model.ctx.dtype == torch.bfloat16 else 4
     widest = 0
-    for b in spec.blocks:
-        m, f = b.mixer, b.feed_forward
-        qkv = getattr(m, "num_heads", 0) * getattr(m, "head_dim", 0) + 2 * getattr(m, "num_kv_heads", 0) * getattr(m, "head_dim", 0)
-        widest = max(widest, 4 * spec.hidden_size * 4 + 4 * qkv * 2 + 6 * getattr(f, "intermediate_size", 0) * 2)
+    for b in model.blocks:
+        per_token = 4 * spec.hidden_size * 4              # residual, two normed copies, a delta
+        inner = b.parts() if callable(getattr(b, "parts", None)) else ()
+        for part in inner:
+            say = getattr(part, "activation_bytes_per_token", None)
+            if callable(say):
+                per_token += int(say(elem))
+            elif callable(getattr(part, "forward", None)) and not hasattr(part, "add_forward"):
+                per_token += 16 * spec.hidden_size * 4
+        widest = max(widest, per_token)
     return max_tokens * widest + 3 * max_rows * spec.vocab_size * 4 + (1 << 30)
 
 
@@ -101,10 +114,13 @@ class Engine:
             per_page = max(1, CacheManager.bytes_per_page(needs, page_size, elem))
             free, total = torch.cuda.mem_get_info(self.device)
             budget = free - int((1.0 - gpu_memory_utilization) * total) \
-                - _activation_reserve_bytes(spec, max_num_batched_tokens, max_running_requests)
+                - _activation_reserve_bytes(self.model, max_num_batched_tokens, max_running_requests)
             num_pages = max(16, budget // per_page)
             # no more than every request slot at full length could use
             num_pages = min(num_pages, max_running_requests * -(-self.max_model_len // page_size))
+        # what the parts allow: a model with a part that cannot be recorded has its steps launched kernel by kernel
+        self.caps = self.model.runtime_caps()
+        cuda_graph = bool(cuda_graph and self.caps.cuda_graph)
         self.cache = CacheManager(needs, page_size, int(num_pages), max_running_requests, self.device, self.dtype,
                                   max_request_tokens=self.max_model_len if cuda_graph else None)
         self.runner = ModelRunner(self.model, self.cache)
@@ -125,6 +141,14 @@ class Engine:
                              if cuda_graph and self.decode_burst > 1 else None)
         self._stats = EngineStats(pages_total=int(num_pages))
         self._next_id = 0
+        # one scheduler for the engine's life: requests arrive and leave while others run
+        self.sched = Scheduler(self.sched_config, CachePoolView(self.cache))
+        self._inbox: deque = deque()                 # (id, prompt, params, time handed in), from any thread
+        self._aborts: deque = deque()
+        self._inbox_lock = threading.Lock()
+        self._submitted_at: Dict[int, float] = {}
+        self._first_token_at: Dict[int, float] = {}
+        self._done: Dict[int, GenerateResult] = {}   # finished requests that nobody has taken yet
 
     # -- the raw step function, for tests and tools ---------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -184,7 +208,118 @@ class Engine:
                 done.append(n)
         return done
 
+    # -- requests that come and go while the engine runs -------------------------------------
+    def submit(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, **options) -> int:
+        """Hand in one request (token ids, sampling options as in ``generate``); returns its id.  The request
+        joins the batch at the next ``step_once``, beside whatever is running, as in the reference's loop
+        (crates/prelude-core/src/engine/run/ar.rs:205-387 drains new requests every iteration; admission
+        :501-558).  May be called from another thread than the one that steps the engine; a run of queued
+        decode steps in flight is cut short so that the newcomer does not wait for all of it."""
+        params = self._params(sampling, options)
+        prompt = list(prompt)
+        vocab = self.model.spec.vocab_size
+        if len(prompt) == 0:
+            raise ValueError("a request needs at least one prompt token")
+        if any((not isinstance(t, int)) or t < 0 or t >= vocab for t in prompt):
+            raise ValueError(f"prompt token ids must be integers in [0, {vocab})")
+        if len(prompt) >= self.max_model_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room below the length limit {self.max_model_len}")
+        with self._inbox_lock:
+            rid = self._next_id
+            self._next_id += 1
+            self._inbox.append((rid, prompt, params, time.perf_counter()))
+        return rid
+
+    def abort(self, request_id: int) -> None:
+        """End a request wherever it is - waiting, in the middle of its prompt, decoding: at the next
+        ``step_once`` its pages and slot go back and its result carries the reason "abort"
+        (ar.rs:436-444).  Unknown and finished ids are ignored.  May be called from another thread."""
+        with self._inbox_lock:
+            self._aborts.append(request_id)
+
+    def has_work(self) -> bool:
+        return bool(self._inbox or self._aborts or self.sched.has_work())
+
+    def _mail_waiting(self) -> bool:
+        return bool(self._inbox or self._aborts)
+
+    def _drain_mail(self) -> None:
+        with self._inbox_lock:
+            arrivals, self._inbox = list(self._inbox), deque()
+            aborts, self._aborts = list(self._aborts), deque()
+        for rid, prompt, params, t_in in arrivals:
+            self.sched.add_request(rid, prompt, params, self.max_model_len)
+            self._submitted_at[rid] = t_in
+        for rid in aborts:
+            self.sched.abort(rid)
+
+    def step_once(self) -> List[GenerateResult]:
+        """One iteration of the loop: take in what was submitted or aborted, schedule a step, run it (or a run of
+        queued decode steps), sample, apply the stop checks, free what finished.  Returns the results of the
+        requests that ended in it."""
+        self._drain_mail()
+        sched = self.sched
+        finished: List[GenerateResult] = []
+        if not sched.has_work():
+            self._collect(finished)
+            return finished
+        try:
+            items = sched.schedule()
+            self._collect(finished)
+            if not items:
+                if sched.has_work():
+                    raise RuntimeError("the scheduler has work but could schedule nothing")
+                return finished
+            burst = self._burst_length(sched, items)
+            if burst >= 2:
+                for j, tokens in enumerate(self._run_burst(items, burst)):
+                    for it, tok in zip(items, tokens):
+                        sched.on_step_done(it if j == 0 else ScheduledItem(it.seq, 1, it.start + j), tok, self.eos_token_ids)
+            else:
+                tokens = self._run_step(items)
+                now = time.perf_counter()
+                for it, tok in zip(items, tokens):
+                    if tok is not None:
+                        self._first_token_at.setdefault(it.seq.request_id, now)
+                    sched.on_step_done(it, tok, self.eos_token_ids)
+        except BaseException:
+            # a step failed (a kernel's status word, an interrupt, ...): what the requests hold goes back, so that
+            # the engine can be used again; their results say "abort"
+            for seq in list(sched.running) + list(sched.waiting):
+                sched.abort(seq.request_id)
+            self._collect(finished)
+            for r in finished:
+                self._done[r.request_id] = r
+            raise
+        self._collect(finished)
+        self._stats.preemptions = sched.stats["preemptions"]
+        return finished
+
+    def run_until_idle(self) -> List[GenerateResult]:
+        """Step until nothing is waiting or running; the results in the order the requests ended."""
+        out: List[GenerateResult] = []
+        while self.has_work():
+            out.extend(self.step_once())
+        return out
+
+    def result(self, request_id: int) -> Optional[GenerateResult]:
+        """The result of a finished request that no ``step_once`` caller has taken (``generate`` keeps the results
+        of requests that are not its own here); None while it runs."""
+        return self._done.pop(request_id, None)
+
     # -- generation ---------------------------------------------------------------------
+    def _params(self, sampling: Optional[SamplingParams], options: Dict[str, object]) -> SamplingParams:
+        q = SamplingParams(**vars(sampling or SamplingParams()))
+        for k in ("max_new_tokens", "temperature", "top_p", "top_k", "seed", "ignore_eos"):
+            if options.get(k) is not None:
+                setattr(q, k, options[k])
+        if options.get("stop_token_ids") is not None:
+            q.stop_token_ids = tuple(options["stop_token_ids"])
+        unknown = set(options) - {"max_new_tokens", "temperature", "top_p", "top_k", "seed", "ignore_eos", "stop_token_ids"}
+        if unknown:
+            raise TypeError(f"unknown sampling options {sorted(unknown)}")
+        return q
+
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                  sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None, *,
                  max_new_tokens: Optional[int] = None, temperature: Optional[float] = None,
@@ -193,82 +328,50 @@ class Engine:
                  ) -> Union[GenerateResult, List[GenerateResult]]:
         """Generate for one prompt (a list of token ids) or several (a list of
         lists).  ``sampling`` gives the options per request or for all; keyword
-        options override it."""
+        options override it.  Built on ``submit`` and ``step_once``: requests that
+        others submit meanwhile run in the same batches."""
         single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
         plist = [list(prompts)] if single else [list(p) for p in prompts]
         if isinstance(sampling, SamplingParams) or sampling is None:
-            plist_params = [sampling or SamplingParams()] * len(plist)
+            plist_params = [sampling] * len(plist)
         else:
             plist_params = list(sampling)
             if len(plist_params) != len(plist):
                 raise ValueError("one SamplingParams per prompt")
-        params = []
-        for p in plist_params:
-            q = SamplingParams(**vars(p))
-            for k, v in (("max_new_tokens", max_new_tokens), ("temperature", temperature), ("top_p", top_p),
-                         ("top_k", top_k), ("seed", seed), ("ignore_eos", ignore_eos)):
-                if v is not None:
-                    setattr(q, k, v)
-            if stop_token_ids is not None:
-                q.stop_token_ids = tuple(stop_token_ids)
-            params.append(q)
-        results = self._run(plist, params)
-        return results[0] if single else results
-
-    def _run(self, prompts: List[List[int]], params: List[SamplingParams]) -> List[GenerateResult]:
-        sched = Scheduler(self.sched_config, CachePoolView(self.cache))
-        t0 = time.perf_counter()
-        ids = []
-        first_token_at: Dict[object, float] = {}
+        options = dict(max_new_tokens=max_new_tokens, temperature=temperature, top_p=top_p, top_k=top_k, seed=seed,
+                       stop_token_ids=stop_token_ids, ignore_eos=ignore_eos)
+        checked = [(p, self._params(sp, options)) for p, sp in zip(plist, plist_params)]
         vocab = self.model.spec.vocab_size
-        for prompt, p in zip(prompts, params):
+        for prompt, _ in checked:                           # all of them before any is handed in
             if any((not isinstance(t, int)) or t < 0 or t >= vocab for t in prompt):
                 raise ValueError(f"prompt token ids must be integers in [0, {vocab})")
-            rid = self._next_id
-            self._next_id += 1
-            sched.add_request(rid, prompt, p, self.max_model_len)
-            ids.append(rid)
-        done: Dict[object, GenerateResult] = {}
+        ids = [self.submit(prompt, q) for prompt, q in checked]
+        mine: Dict[int, GenerateResult] = {}
         try:
-            while sched.has_work():
-                items = sched.schedule()
-                self._collect(sched, done, first_token_at, t0)
-                if not items:
-                    if sched.has_work():
-                        raise RuntimeError("the scheduler has work but could schedule nothing")
-                    break
-                burst = self._burst_length(sched, items)
-                if burst >= 2:
-                    for j, tokens in enumerate(self._run_burst(items, burst)):
-                        for it, tok in zip(items, tokens):
-                            sched.on_step_done(it if j == 0 else ScheduledItem(it.seq, 1, it.start + j), tok, self.eos_token_ids)
-                    self._collect(sched, done, first_token_at, t0)
-                    continue
-                tokens = self._run_step(items)
-                now = time.perf_counter()
-                for it, tok in zip(items, tokens):
-                    if tok is not None and it.seq.request_id not in first_token_at:
-                        first_token_at[it.seq.request_id] = now
-                    sched.on_step_done(it, tok, self.eos_token_ids)
-                self._collect(sched, done, first_token_at, t0)
+            while len(mine) < len(ids):
+                if not self.has_work():
+                    raise RuntimeError("requests are unfinished and the engine has no work")
+                for r in self.step_once():
+                    if r.request_id in ids:
+                        mine[r.request_id] = r
+                    else:
+                        self._done[r.request_id] = r
         except BaseException:
-            # a step failed (a kernel's status word, an interrupt, ...): what the unfinished requests hold goes back,
-            # so that the engine can be used again
             for rid in ids:
-                if rid not in done:
-                    sched.abort(rid)
-            sched.drain_finished()
+                self._done.pop(rid, None)
             raise
-        self._stats.preemptions += sched.stats["preemptions"]
-        return [done[r] for r in ids]
+        results = [mine[r] for r in ids]
+        return results[0] if single else results
 
-    def _collect(self, sched: Scheduler, done, first_token_at, t0) -> None:
+    def _collect(self, into: List[GenerateResult]) -> None:
         now = time.perf_counter()
-        for seq in sched.drain_finished():
-            done[seq.request_id] = GenerateResult(
-                seq.request_id, list(seq.output), seq.finish_reason or "abort", len(seq.prompt), len(seq.output),
-                ttft_ms=(first_token_at.get(seq.request_id, now) - t0) * 1e3, total_ms=(now - t0) * 1e3,
-                preemptions=seq.preempt_count)
+        for seq in self.sched.drain_finished():
+            rid = seq.request_id
+            t0 = self._submitted_at.pop(rid, now)
+            first = self._first_token_at.pop(rid, now)
+            into.append(GenerateResult(
+                rid, list(seq.output), seq.finish_reason or "abort", len(seq.prompt), len(seq.output),
+                ttft_ms=(first - t0) * 1e3, total_ms=(now - t0) * 1e3, preemptions=seq.preempt_count))
 
     def _burst_length(self, sched: Scheduler, items) -> int:
         """How many decode steps may be queued on the device without the host looking at the
@@ -279,7 +382,7 @@ class Engine:
         waiting, sampling runs on the device (greedy or temperature), every request still has
         that many tokens to go (one that stops early - end of sequence, a stop token - has
         its later tokens dropped), and the pages for all of it are free."""
-        if self.burst_graphs is None or sched.waiting or len(items) != len(sched.running):
+        if self.burst_graphs is None or sched.waiting or len(items) != len(sched.running) or self._mail_waiting():
             return 1
         if not all(it.n_tokens == 1 and it.samples for it in items):
             return 1
@@ -313,7 +416,15 @@ class Engine:
         g.load([e.tokens[0] for e in entries], starts, [self.cache.slot_of(e.request_id) for e in entries],
                [it.seq.params.temperature for it in items], [it.seq.params.seed for it in items],
                [len(it.seq.output) for it in items])
-        steps = g.replay_burst(k)
+        steps = g.replay_burst(k, stop=self._mail_waiting)
+        if len(steps) < k:
+            # the run was cut short (somebody arrived or was aborted): the cache holds what the steps that ran wrote
+            k = len(steps)
+            for it in items:
+                self.cache.rewind(it.seq.request_id, it.start + k)
+        now = time.perf_counter()
+        for it in items:
+            self._first_token_at.setdefault(it.seq.request_id, now)
         for e in entries:
             self.cache.trim(e.request_id)
         st = self._stats
@@ -359,9 +470,7 @@ class Engine:
         else:
             logits = self.runner.step(entries, check_status=False)
             sampled = self.sampler.sample(logits, temps, top_ks, top_ps, seeds, counters) if rows else []
-            code = int(self.runner.last_batch.status.item())
-            if code != 0:
-                raise RuntimeError(f"a kernel met a bad page id or position during the step (code {code})")
+            raise_on_status(int(self.runner.last_batch.status.item()))
         st.steps += 1
         st.decode_steps += 1 if decode_only else 0
         st.generated_tokens += len(rows)

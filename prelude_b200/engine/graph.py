@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 from ..ops import kernels as K
-from .batch import StepBatch
+from .batch import StepBatch, raise_on_status
 from .capture import no_collection
 
 
@@ -40,81 +40,97 @@ class DecodeGraph:
             raise RuntimeError("captured decode needs device-resident block tables (max_request_tokens)")
         dev = runner.device
         bs = batch_size
-        # int32 block: tokens | positions | slots | logit_rows(arange) | cu_q(arange) | status
-        self.n_int = 3 * bs
-        self.ints = torch.zeros(5 * bs + 2, dtype=torch.int32, device=dev)
-        self.ints[3 * bs:4 * bs] = torch.arange(bs, dtype=torch.int32, device=dev)
-        self.ints[4 * bs:5 * bs + 1] = torch.arange(bs + 1, dtype=torch.int32, device=dev)
-        self.tokens, self.positions, self.slots = self.ints[0:bs], self.ints[bs:2 * bs], self.ints[2 * bs:3 * bs]
-        self.status = self.ints[5 * bs + 1:5 * bs + 2]
-        self.temps = torch.zeros(bs, dtype=torch.float32, device=dev)
-        self.seeds = torch.zeros(bs, dtype=torch.int64, device=dev)
-        self.counters = torch.zeros(bs, dtype=torch.int64, device=dev)
-        self.sampled = torch.zeros(bs, dtype=torch.int32, device=dev)
-        self.host_ints = torch.zeros(3 * bs, dtype=torch.int32, pin_memory=True)
-        self.host_samp = torch.zeros(3 * bs, dtype=torch.int64, pin_memory=True)   # temps bits | seeds | counters
-        self.dev_samp = torch.zeros(3 * bs, dtype=torch.int64, device=dev)
-        self.host_out = torch.zeros(bs + 1, dtype=torch.int32, pin_memory=True)
+        # One device buffer holds everything that changes from step to step, so that one host-to-device copy fills it:
+        #   seeds int64 [bs] | counters int64 [bs] | temperatures float32 [bs] |
+        #   tokens | positions | kv_len | slots (int32 [bs] each) | status int32 [1] | sampled int32 [bs]
+        # (status and the sampled tokens side by side: one device-to-host copy reads both)
+        # and behind it what never changes: 0..bs-1 (the request of every token, and the rows whose logits are
+        # wanted) and 0..bs (cumulative query lengths).
+        self.n_loaded = 8 * bs + 8 * bs + 4 * bs + 4 * (5 * bs + 1)
+        total = self.n_loaded + 4 * (2 * bs + 1)
+        self.buf = torch.zeros(total, dtype=torch.uint8, device=dev)
+        self.host_buf = torch.zeros(self.n_loaded, dtype=torch.uint8, pin_memory=True)
+
+        def views(b):
+            o = 0
+            seeds = b[o:o + 8 * bs].view(torch.int64); o += 8 * bs
+            counters = b[o:o + 8 * bs].view(torch.int64); o += 8 * bs
+            temps = b[o:o + 4 * bs].view(torch.float32); o += 4 * bs
+            ints = b[o:o + 4 * (5 * bs + 1)].view(torch.int32)
+            return seeds, counters, temps, ints
+
+        self.seeds, self.counters, self.temps, self.ints = views(self.buf)
+        self._h_seeds, self._h_counters, self._h_temps, self._h_ints = (t.numpy() for t in views(self.host_buf))
+        fixed = self.buf[self.n_loaded:].view(torch.int32)
+        fixed[:bs] = torch.arange(bs, dtype=torch.int32, device=dev)
+        fixed[bs:] = torch.arange(bs + 1, dtype=torch.int32, device=dev)
+        self.tokens, self.positions = self.ints[0:bs], self.ints[bs:2 * bs]
+        self.kv_len, self.slots = self.ints[2 * bs:3 * bs], self.ints[3 * bs:4 * bs]
+        self.status = self.ints[4 * bs:4 * bs + 1]
+        self.sampled = self.ints[4 * bs + 1:5 * bs + 1]
+        self.host_out = torch.zeros(bs + 1, dtype=torch.int32, pin_memory=True)     # status | sampled
+        self._events: List[torch.cuda.Event] = []
         self.host_burst: Optional[torch.Tensor] = None      # [steps, bs] sampled tokens of a queued run of replays
+        # The batch means what a launched decode step's batch means: a token's request is its index in the batch,
+        # kv_len counts the token itself, the host copies are filled by load().  What differs is where the block
+        # tables live: the device-resident ones have a row per state slot.
         self.batch = StepBatch(
-            n_tokens=bs, n_seqs=bs, token_ids=self.tokens, positions=self.positions, token_seq=self.slots,
-            cu_q=self.ints[4 * bs:5 * bs + 1], q_start=self.positions, kv_len=self.positions,
-            state_slots=self.slots, logit_rows=self.ints[3 * bs:4 * bs], block_tables=dict(cache.device_tables),
-            status=self.status, q_lens=np.ones(bs, np.int32), max_q_len=1, decode_only=True)
+            n_tokens=bs, n_seqs=bs, token_ids=self.tokens, positions=self.positions, token_seq=fixed[:bs],
+            cu_q=fixed[bs:], q_start=self.positions, kv_len=self.kv_len, state_slots=self.slots,
+            logit_rows=fixed[:bs], block_tables=dict(cache.device_tables), status=self.status,
+            token_table_row=self.slots, q_lens=np.ones(bs, np.int32), q_start_host=np.zeros(bs, np.int32),
+            kv_len_host=np.ones(bs, np.int32), state_slots_host=np.zeros(bs, np.int32), max_q_len=1, decode_only=True)
         self.batch.extras["captured"] = True
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches = 0
         self.logits: Optional[torch.Tensor] = None
 
     def _body(self) -> None:
-        # temps travel as the low 32 bits of an int64 word
-        self.temps.copy_(self.dev_samp[:self.bs].to(torch.int32).view(torch.float32))
-        self.seeds.copy_(self.dev_samp[self.bs:2 * self.bs])
-        self.counters.copy_(self.dev_samp[2 * self.bs:])
         self.logits = self.runner.model.forward(self.batch, self.runner.caches)
-        out = K.sample(self.logits, self.temps, self.seeds, self.counters)
-        self.sampled.copy_(out)
+        K.sample(self.logits, self.temps, self.seeds, self.counters, out=self.sampled)
         if self.self_feeding:
-            K.decode_advance(self.tokens, self.positions, None, self.sampled, self.runner.model.spec.max_positions)
-            self.dev_samp[2 * self.bs:] += 1
+            K.decode_advance(self.tokens, self.positions, self.kv_len, self.counters, self.sampled,
+                             self.runner.model.spec.max_positions)
 
     def capture(self) -> None:
         """Warm up once eagerly on the current buffer contents, then capture."""
         from ..ops import library
-        saved, saved_samp = self.ints.clone(), self.dev_samp.clone()
+        saved = self.buf.clone()
         stream = torch.cuda.Stream(device=self.runner.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             self._body()
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
-        self.ints.copy_(saved)          # a self-feeding warm-up has moved tokens, positions and counters
-        self.dev_samp.copy_(saved_samp)
+        self.buf.copy_(saved)           # a self-feeding warm-up has moved tokens, positions and counters
         before = library.launch_count
         graph = torch.cuda.CUDAGraph()
         with no_collection(), torch.cuda.graph(graph):
             self._body()
         self.launches = library.launch_count - before
         self.graph = graph
-        self.ints.copy_(saved)
-        self.dev_samp.copy_(saved_samp)
+        self.buf.copy_(saved)
 
     def load(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
              temperatures: Sequence[float], seeds: Sequence[int], counters: Sequence[int]) -> None:
-        """Fill the fixed buffers for the next replay (two small host-to-device copies)."""
+        """Fill the fixed buffers for the next replay (one host-to-device copy).  The status word travels with
+        them as zero, so a code that a kernel raised in an earlier step does not outlive it."""
         bs = self.bs
-        h = self.host_ints.numpy()
-        h[0:bs], h[bs:2 * bs], h[2 * bs:3 * bs] = tokens, positions, slots
-        s = self.host_samp.numpy()
-        s[0:bs] = np.asarray(temperatures, dtype=np.float32).view(np.int32).astype(np.int64)
-        s[bs:2 * bs] = [x & (2**63 - 1) for x in seeds]
-        s[2 * bs:] = counters
-        self.ints[:3 * bs].copy_(self.host_ints, non_blocking=True)
-        self.dev_samp.copy_(self.host_samp, non_blocking=True)
+        h = self._h_ints
+        h[0:bs], h[bs:2 * bs], h[3 * bs:4 * bs] = tokens, positions, slots
+        h[2 * bs:3 * bs] = h[bs:2 * bs] + 1                 # tokens in the cache after this step
+        h[4 * bs] = 0
+        self._h_temps[:] = temperatures
+        self._h_seeds[:] = [x & (2**63 - 1) for x in seeds]
+        self._h_counters[:] = counters
+        self.buf[:self.n_loaded].copy_(self.host_buf, non_blocking=True)
+        b = self.batch
+        b.q_start_host, b.kv_len_host = h[bs:2 * bs].copy(), h[2 * bs:3 * bs].copy()
+        b.state_slots_host = h[3 * bs:4 * bs].copy()
 
     @property
     def h2d_bytes(self) -> int:
-        return self.host_ints.numel() * 4 + self.host_samp.numel() * 8
+        return self.host_buf.numel()
 
     @property
     def d2h_bytes(self) -> int:
@@ -125,31 +141,39 @@ class DecodeGraph:
             self.capture()
         self.graph.replay()
 
-    def replay_burst(self, steps: int) -> List[List[int]]:
-        """Queue ``steps`` replays of a self-feeding graph - every step's input is the step before's
-        output, on the device - and return the sampled tokens of every step.  The host waits once."""
+    def replay_burst(self, steps: int, stop=None, ahead: int = 3) -> List[List[int]]:
+        """Queue up to ``steps`` replays of a self-feeding graph - every step's input is the step before's
+        output, on the device - and return the sampled tokens of the steps that ran.  No more than ``ahead``
+        replays are queued beyond the one the device is working on; before each further one the host asks
+        ``stop()`` and ends the run early when it says so (a request has arrived or been aborted meanwhile)."""
         if not self.self_feeding:
             raise RuntimeError("a run of replays needs a self-feeding graph")
         if self.host_burst is None or self.host_burst.shape[0] < steps:
             self.host_burst = torch.zeros((max(steps, 8), self.bs), dtype=torch.int32, pin_memory=True)
+        while len(self._events) < steps:
+            self._events.append(torch.cuda.Event())
+        ran = 0
         for j in range(steps):
+            if j >= ahead:
+                self._events[j - ahead].synchronize()
+                if stop is not None and stop():
+                    break
             self.replay()
             self.host_burst[j].copy_(self.sampled, non_blocking=True)   # in stream order, before the next replay overwrites it
-        self.host_out[self.bs:].copy_(self.status, non_blocking=True)
+            self._events[j].record()
+            ran += 1
+        self.host_out[:1].copy_(self.status, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        if int(self.host_out[self.bs]) != 0:
-            raise RuntimeError(f"a kernel met a bad page id or position during the step (code {int(self.host_out[self.bs])})")
-        return self.host_burst[:steps].tolist()
+        raise_on_status(int(self.host_out[0]))
+        return self.host_burst[:ran].tolist()
 
     def fetch(self) -> List[int]:
         """Sampled tokens of the last replay (one device-to-host copy, then a wait)."""
-        self.host_out[:self.bs].copy_(self.sampled, non_blocking=True)
-        self.host_out[self.bs:].copy_(self.status, non_blocking=True)
+        self.host_out.copy_(self.ints[4 * self.bs:], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         out = self.host_out.tolist()
-        if out[-1] != 0:
-            raise RuntimeError(f"a kernel met a bad page id or position during the step (code {out[-1]})")
-        return out[:-1]
+        raise_on_status(out[0])
+        return out[1:]
 
 
 class DecodeGraphs:

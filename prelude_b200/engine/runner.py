@@ -25,7 +25,7 @@ from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
 from ..ops.library import KernelLibraryError, require_device
 from ..parts.model import DecoderModel
-from .batch import StepBatch, StepItem, build_step_batch
+from .batch import StepBatch, StepError, StepItem, build_step_batch, raise_on_status
 
 
 @dataclass
@@ -34,10 +34,6 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
-
-
-class StepError(RuntimeError):
-    """A kernel reported a bad page or position during the step."""
 
 
 class ModelRunner:
@@ -123,14 +119,16 @@ class ModelRunner:
                                      spec.max_positions)
             self.cache.zero_fresh_state()
             logits = self.model.forward(batch, self.caches)
+            if self.cache.device_tables:
+                # a launched step reads the tables it was given; the device-resident ones are kept up to date all
+                # the same, so that what is queued for them stays short and a later captured step finds them current
+                self.cache.flush_table_updates()
         for r in rids:
             self.cache.trim(r)
         self.steps_run += 1
         self.last_batch = batch
         if check_status:
-            code = int(batch.status.item())
-            if code != 0:
-                raise StepError(f"a kernel met a bad page id or position during the step (code {code})")
+            raise_on_status(int(batch.status.item()))
         return logits
 
     def finish(self, request_id: Hashable) -> None:

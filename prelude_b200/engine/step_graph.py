@@ -90,15 +90,16 @@ class StepGraph:
         dev = runner.device
         R = cache.max_slots
         self.max_requests = R
-        # int32 block: tokens | positions | token rows | cu_q | q_start | kv_len | slots | logit rows | status
-        sizes = [bucket, bucket, bucket, R + 1, R, R, R, bucket, 1]
+        # int32 block: tokens | positions | token rows | cu_q | q_start | kv_len | slots | logit rows | status | token requests
+        sizes = [bucket, bucket, bucket, R + 1, R, R, R, bucket, 1, bucket]
         self.offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
         self.ints = torch.zeros(int(self.offsets[-1]), dtype=torch.int32, device=dev)
         self.host = torch.zeros(int(self.offsets[-1]), dtype=torch.int32, pin_memory=True)
         v = [self.ints[int(self.offsets[i]):int(self.offsets[i + 1])] for i in range(len(sizes))]
         self.batch = StepBatch(
-            n_tokens=bucket, n_seqs=0, token_ids=v[0], positions=v[1], token_seq=v[2], cu_q=v[3], q_start=v[4],
-            kv_len=v[5], state_slots=v[6], logit_rows=v[7][:0], block_tables=dict(cache.device_tables), status=v[8])
+            n_tokens=bucket, n_seqs=0, token_ids=v[0], positions=v[1], token_seq=v[9], cu_q=v[3], q_start=v[4],
+            kv_len=v[5], state_slots=v[6], logit_rows=v[7][:0], block_tables=dict(cache.device_tables), status=v[8],
+            token_table_row=v[2])
         self._logit_rows = v[7]
         self.recorder = _Recorder(pool, stream)
         self.delta = self.res = None
@@ -123,6 +124,8 @@ class StepGraph:
         h[o[5]:o[5] + R] = kv_len
         h[o[6]:o[6] + R] = slots
         h[o[7]:o[7] + len(rows)] = rows
+        h[o[9]:o[10]] = -1
+        h[o[9]:o[9] + T] = np.repeat(np.arange(R, dtype=np.int32), q_lens)   # a token's request, as in a launched step
         self.ints.copy_(self.host, non_blocking=True)
         keep = {k: val for k, val in b.extras.items() if k == "recorder" or (isinstance(k, tuple) and k and k[0] == "workspace")}
         b.extras.clear()

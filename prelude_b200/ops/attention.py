@@ -131,7 +131,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         out = torch.empty_like(q)
     if q.dtype != torch.bfloat16 or not tensor_core_shape_ok(nH, nKV, D, batch.decode_only, page_size):
         n = batch.n_real                                   # the rows after them are padding of a captured step
-        out[:n] = K.paged_attention_ref(q[:n], k_pages, v_pages, batch.positions[:n], batch.token_seq[:n], table, scale,
+        out[:n] = K.paged_attention_ref(q[:n], k_pages, v_pages, batch.positions[:n], batch.table_row_of_token[:n], table, scale,
                                         window, batch.status)
         return out
     lib = _l.library()
@@ -157,7 +157,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         row = nH * D * q.element_size()
         check(lib.pb_attention_decode_bf16(
             q.data_ptr() + t0 * row, k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr() + t0 * row, table.data_ptr(),
-            table.shape[1], batch.positions.data_ptr() + 4 * t0, batch.token_seq.data_ptr() + 4 * t0, page_size, num_pages,
+            table.shape[1], batch.positions.data_ptr() + 4 * t0, batch.table_row_of_token.data_ptr() + 4 * t0, page_size, num_pages,
             n, nH, nKV, D, float(scale), win, swizzled, splits, scratch.data_ptr() if splits > 1 else None,
             _decode_counters(q.device).data_ptr() if splits > 1 else None, batch.status.data_ptr(), stream), "attention_decode")
 
@@ -182,14 +182,14 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         if n_tiles:
             check(lib.pb_attention_prefill_tc_bf16(
                 q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
-                batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+                batch.positions.data_ptr(), batch.table_row_of_token.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
                 tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
                 swizzled, batch.status.data_ptr(), stream), "attention_prefill_tc")
     tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, 64 // (nH // nKV), mma_min, tc_min)
     if n_tiles:
         check(lib.pb_attention_prefill_bf16(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
-            batch.positions.data_ptr(), batch.token_seq.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+            batch.positions.data_ptr(), batch.table_row_of_token.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
             tile_seq.data_ptr(), tile_tok0.data_ptr(), n_tiles, page_size, num_pages, T, nH, nKV, D, float(scale), win,
             swizzled, batch.status.data_ptr(), stream), "attention_prefill")
     return out

@@ -275,8 +275,10 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor) -> torch.Tensor:
-    """One token per row: greedy where temperature < 1e-7, else a Philox draw from softmax(logits / T)."""
+def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row: greedy where temperature < 1e-7, else a Philox draw from softmax(logits / T).
+    The tokens go to ``out`` (int32 [rows]) when given."""
     _need(logits, "logits", torch.float32, contiguous=False)
     _need(temperature, "temperature", torch.float32)
     _need(seeds, "seeds", torch.int64)
@@ -284,7 +286,12 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor,
     rows, vocab = logits.shape
     if not (temperature.numel() == seeds.numel() == counters.numel() == rows):
         raise KernelLibraryError("sample: one temperature, seed and counter per row")
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    else:
+        _need(out, "out", torch.int32)
+        if out.numel() != rows:
+            raise KernelLibraryError("sample: out holds one token per row")
     lib = _l.library()
     scratch = torch.empty(max(1, lib.pb_sample_scratch_floats(rows, vocab)), dtype=torch.float32, device=logits.device)
     check(lib.pb_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(), seeds.data_ptr(),
@@ -318,13 +325,15 @@ def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, status:
                                       _ptr(status), _stream()), "scatter_i32")
 
 
-def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, counters: Optional[torch.Tensor],
-                   sampled: torch.Tensor, max_positions: int) -> None:
-    """tokens = sampled; positions += 1; counters += 1: a decode step that feeds itself."""
+def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: Optional[torch.Tensor],
+                   counters: Optional[torch.Tensor], sampled: torch.Tensor, max_positions: int) -> None:
+    """tokens = sampled; positions += 1; kv_len = positions + 1; counters += 1: a decode step that feeds itself."""
     _need(tokens, "tokens", torch.int32)
     _need(positions, "positions", torch.int32)
     _need(sampled, "sampled", torch.int32)
+    if kv_len is not None:
+        _need(kv_len, "kv_len", torch.int32)
     if counters is not None:
         _need(counters, "counters", torch.int64)
-    check(_l.library().pb_decode_advance(tokens.data_ptr(), positions.data_ptr(), _ptr(counters), sampled.data_ptr(),
-                                         tokens.numel(), int(max_positions), _stream()), "decode_advance")
+    check(_l.library().pb_decode_advance(tokens.data_ptr(), positions.data_ptr(), _ptr(kv_len), _ptr(counters),
+                                         sampled.data_ptr(), tokens.numel(), int(max_positions), _stream()), "decode_advance")

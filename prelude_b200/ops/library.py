@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 
 class KernelLibraryError(RuntimeError):
@@ -55,7 +55,7 @@ _SIGNATURES = {
     "pb_gemm_tc_scratch_bytes": ([I, I, I], L),
     "pb_gemm_tc_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, P, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
-    "pb_decode_advance": ([P, P, P, P, I, I, P], I),
+    "pb_decode_advance": ([P, P, P, P, P, I, I, P], I),
 }
 
 _lock = threading.Lock()

@@ -16,6 +16,7 @@ bfloat16, float32 accumulation:
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from typing import Dict, List, Optional
 
@@ -123,10 +124,27 @@ def gated_mlp_chain(x: torch.Tensor, weight_gate_up: torch.Tensor, weight_down: 
 
 _tc_scratch: Dict[torch.device, torch.Tensor] = {}
 _tc_status: Dict[torch.device, torch.Tensor] = {}
+_step_status: Optional[torch.Tensor] = None
+
+
+@contextlib.contextmanager
+def step_status(status: Optional[torch.Tensor]):
+    """While this is open, the products raise ``status`` (the status word of the step being run, which the engine
+    reads after every step) instead of the device's own word: a product that gave up a wait then fails the step
+    like any other kernel's complaint, instead of passing unseen."""
+    global _step_status
+    before, _step_status = _step_status, status
+    try:
+        yield
+    finally:
+        _step_status = before
 
 
 def tc_status(device: torch.device) -> torch.Tensor:
-    """The status word of this library's products on this device (non-zero: a block gave up waiting)."""
+    """The status word that this library's products raise (non-zero: a block gave up waiting): the running step's
+    while a model runs one, else one word per device for products called on their own."""
+    if _step_status is not None:
+        return _step_status
     st = _tc_status.get(device)
     if st is None:
         st = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)

@@ -35,6 +35,9 @@ class Attention:
         self.kv_cols = spec.num_kv_heads * spec.head_dim
         self.w_qkv = self.w_o = self.b_qkv = self.b_o = self.q_norm = self.k_norm = None
 
+    def parts(self):
+        return (self.position,)
+
     # -- weights ----------------------------------------------------------------
     def tensors(self) -> Dict[str, TensorReq]:
         s, p = self.spec, self.prefix
@@ -76,6 +79,10 @@ class Attention:
             self.q_norm, self.k_norm = vec("q_norm.weight"), vec("k_norm.weight")
         self.position.load(get, ctx)
 
+    def activation_bytes_per_token(self, elem: int) -> int:
+        """The merged projection, q, the attention output (twice: the layers share one buffer, a step keeps one)."""
+        return (2 * self.q_cols + 2 * self.kv_cols + 2 * self.q_cols) * elem + self.spec.hidden_size * elem
+
     # -- cache ------------------------------------------------------------------
     def cache_need(self) -> KvPagesNeed:
         return KvPagesNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
@@ -91,7 +98,7 @@ class Attention:
         q = K.qknorm_rope_kvwrite(
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm,
             s.qk_norm_eps if s.qk_norm_eps is not None else 0.0, self.position.cos, self.position.sin,
-            self.position.rotary_dim, batch.positions, batch.token_seq, table, cache.k_pages, cache.v_pages,
+            self.position.rotary_dim, batch.positions, batch.table_row_of_token, table, cache.k_pages, cache.v_pages,
             write_cache, batch.status, out=batch.workspace("attention_q", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype))
         o = paged_attention(q, cache.k_pages, cache.v_pages, batch, cache.group, s.softmax_scale, s.window,
                             out=batch.workspace("attention_out", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype))

@@ -46,6 +46,10 @@ class GatedMlp:
         self.w_gate_up = torch.cat([mat("gate_proj.weight"), mat("up_proj.weight")], dim=0).contiguous()
         self.w_down = mat("down_proj.weight").contiguous()
 
+    def activation_bytes_per_token(self, elem: int) -> int:
+        """The merged gate/up projection, the activation, the output (as float32 partial sums at most)."""
+        return 3 * self.spec.intermediate_size * elem + 4 * self.spec.hidden_size * 4
+
     def forward(self, x: torch.Tensor):
         """The feed-forward of x; what comes back goes to a fused residual add, which also takes
         the partial sums of a product whose K was cut into parts."""

@@ -1,5 +1,6 @@
 """The decoder: embedding, blocks run in the order the spec lists, final norm,
-output head (crates/prelude-core/src/models/qwen3.rs:534-678).
+output head (crates/prelude-core/src/models/qwen3.rs:534-678).  All four are
+parts chosen by the spec; this file only says in which order they run.
 
 ``DecoderModel(spec)`` is cheap; ``tensors()`` says what it needs;
 ``load(store, ctx)`` checks the store against that list in one go and moves the
@@ -14,14 +15,15 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import step_status
 from ..weights.loader import TensorReq, WeightStore
 from . import attention as _attention  # noqa: F401  (registers the part)
 from . import block as _block  # noqa: F401
+from . import ends as _ends  # noqa: F401
 from . import mlp as _mlp  # noqa: F401
 from . import norm as _norm  # noqa: F401
 from . import rope as _rope  # noqa: F401
-from .registry import RunContext, make_part
+from .registry import KvPagesNeed, RunContext, RuntimeCaps, StateNeed, capturable, make_part
 
 
 class DecoderModel:
@@ -30,37 +32,42 @@ class DecoderModel:
         self.order = spec.resolved_order()
         self.blocks = [make_part("block", b, b.prefix) for b in spec.blocks]
         self.final_norm = make_part("norm", spec.final_norm, spec.final_norm_name)
-        self.embed: Optional[torch.Tensor] = None
-        self.head: Optional[torch.Tensor] = None
+        self.embedding = make_part("embedding", spec.embedding_spec(), "")
+        self.head = make_part("head", spec.head_spec(), "")
         self.ctx: Optional[RunContext] = None
 
     # -- weights ------------------------------------------------------------------
     def tensors(self) -> Tuple[Dict[str, TensorReq], Dict[str, TensorReq]]:
         """(required, optional) tensors by name."""
-        s = self.spec
-        req: Dict[str, TensorReq] = {s.embed_name: TensorReq((s.vocab_size, s.hidden_size))}
-        opt: Dict[str, TensorReq] = {}
+        req: Dict[str, TensorReq] = dict(self.embedding.tensors())
         for b in self.blocks:
             req.update(b.tensors())
         req.update(self.final_norm.tensors())
-        # a tied model may still carry a copy of the head; it is not read
-        (opt if s.tie_embeddings else req)[s.head_name] = TensorReq((s.vocab_size, s.hidden_size))
-        return req, opt
+        head_req, opt = self.head.tensors()
+        req.update(head_req)
+        return req, dict(opt)
 
     def load(self, store: WeightStore, ctx: RunContext) -> "DecoderModel":
         req, opt = self.tensors()
-        store.check(req, opt)
+        store.check(req, opt, self.spec.ignored_tensors)
         self.ctx = ctx
-        s = self.spec
-        self.embed = store.get(s.embed_name).to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        self.embedding.load(store.get, ctx)
         for b in self.blocks:
             b.load(store.get, ctx)
         self.final_norm.load(store.get, ctx)
-        if s.tie_embeddings:
-            self.head = self.embed                      # the same memory (qwen3.rs:639-641)
-        else:
-            self.head = store.get(s.head_name).to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        self.head.load(store.get, ctx, self.embedding)
         return self
+
+    def all_parts(self):
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def runtime_caps(self) -> RuntimeCaps:
+        """What the engine may do with this model, from what its parts say."""
+        needs = self.cache_needs()
+        pages = any(isinstance(n, KvPagesNeed) for n in needs)
+        return RuntimeCaps(kv_cache=pages, paged_attention=pages, varlen=True,
+                           state_slots=any(isinstance(n, StateNeed) for n in needs),
+                           cuda_graph=all(capturable(p) for p in self.all_parts()))
 
     # -- cache needs, one per entry of the run order ---------------------------------
     def cache_needs(self) -> List[object]:
@@ -99,10 +106,11 @@ class DecoderModel:
         """The layers: returns (delta, res), the last layer's output and the residual it has yet to be added to.
         Every launch in here has the shape of the step's token count alone, except what a mixer runs through
         ``batch.extras["recorder"]``; that is what lets a step be captured piece by piece."""
-        res = K.embed_gather(batch.token_ids, self.embed)
-        delta = None
-        for call in self.order:
-            delta = self.blocks[call.block].forward(delta, res, batch, caches[call.cache], call.writes_cache)
+        with step_status(batch.status):
+            res = self.embedding.forward(batch)
+            delta = None
+            for call in self.order:
+                delta = self.blocks[call.block].forward(delta, res, batch, caches[call.cache], call.writes_cache)
         return delta, res
 
     def head_logits(self, delta, res, batch) -> torch.Tensor:
@@ -110,4 +118,5 @@ class DecoderModel:
         if batch.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=res.device)
         x = self.final_norm.gather_add_forward(delta, res, batch.logit_rows)
-        return linear(x, self.head, None, out_dtype=torch.float32)
+        with step_status(batch.status):
+            return self.head.forward(x)

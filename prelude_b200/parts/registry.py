@@ -19,6 +19,16 @@ Families and the calls the model makes on their members:
   block         ``forward(delta, res, batch, cache, write_cache) -> delta'``: ``res``
                 is the float32 residual stream, updated in place; ``delta`` is what
                 the previous block left to be added (None for the first).
+  embedding     ``forward(batch) -> res``: the float32 residual stream [T, hidden] that
+                the step's tokens start from; ``table`` is what a tied head may take.
+  head          ``tensors() -> (required, optional)``, ``load(get, ctx, embedding)`` and
+                ``forward(x) -> logits``: x [W, hidden] are the wanted rows after the
+                final norm, logits float32 [W, vocab].
+
+Any part may carry ``capturable = False``: it then decides on the host from data that
+only the device has during a replay (a loop over requests, a branch on a value), so a
+step through it cannot be recorded as a CUDA graph; the engine launches such a model's
+steps kernel by kernel (``RuntimeCaps.cuda_graph``).
 
 A part takes every size and constant from its spec and never looks at the
 model around it.  A new part: write its spec dataclass with a ``kind`` string,
@@ -31,7 +41,7 @@ from typing import Callable, Dict, Optional, Tuple
 
 import torch
 
-FAMILIES = ("norm", "position", "mixer", "feed_forward", "block")
+FAMILIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
 _PARTS: Dict[Tuple[str, str], type] = {}
 
 
@@ -68,6 +78,27 @@ class RunContext:
     products on the float32 units) or torch.bfloat16 (the serving path)."""
     device: torch.device
     dtype: torch.dtype
+
+
+@dataclass(frozen=True)
+class RuntimeCaps:
+    """What the engine may do with a model, put together from what its parts say
+    (the reference keeps the same record per architecture,
+    crates/prelude-core/src/engine/types.rs:152-160, and switches captured steps
+    off where a part cannot be recorded, crates/prelude-cuda/src/executor.rs:38-42)."""
+    kv_cache: bool            # some layer keeps keys and values in pages
+    paged_attention: bool     # ... and reads them through block tables
+    varlen: bool              # steps may mix portions of different lengths (every part here takes ragged batches)
+    state_slots: bool         # some layer keeps fixed-size state per request
+    cuda_graph: bool          # every part can be recorded: decode steps and prompt steps may be captured
+
+
+def capturable(part) -> bool:
+    """Whether a part (and the parts it is made of, which it lists in ``parts()``) can be recorded in a CUDA graph."""
+    if not getattr(part, "capturable", True):
+        return False
+    inner = getattr(part, "parts", None)
+    return all(capturable(p) for p in inner()) if callable(inner) else True
 
 
 @dataclass(frozen=True)

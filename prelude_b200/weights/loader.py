@@ -102,13 +102,20 @@ class WeightStore:
             raise WeightError(self.source, [name], [], [])
         return normalize_storage(self._where[name].tensor(name))
 
-    def check(self, required: Mapping[str, TensorReq], optional: Mapping[str, TensorReq] = None) -> None:
+    def check(self, required: Mapping[str, TensorReq], optional: Mapping[str, TensorReq] = None,
+              ignored: Iterable[str] = ()) -> None:
         """Raise one WeightError unless the store holds exactly the required
-        tensors (plus any of the optional ones) with the stated shapes."""
+        tensors (plus any of the optional ones) with the stated shapes.  ``ignored``
+        are name patterns (shell style: ``*.rotary_emb.inv_freq``) of tensors that a
+        checkpoint of the architecture may carry and the model never reads; they are
+        passed over instead of counting as unexpected."""
+        import fnmatch
         optional = optional or {}
+        patterns = list(ignored)
         have = set(self.names())
         missing = sorted(n for n in required if n not in have)
-        unexpected = sorted(n for n in have if n not in required and n not in optional)
+        unexpected = sorted(n for n in have if n not in required and n not in optional
+                            and not any(fnmatch.fnmatchcase(n, pat) for pat in patterns))
         wrong, wrong_type = [], []
         for name, req in list(required.items()) + list(optional.items()):
             if name in have:

@@ -169,8 +169,9 @@ def decoder_block(res: torch.Tensor, w, i: int, cfg: dict, cos, sin, kv_from=Non
 # ----------------------------------------------------------------------------
 def forward_logits(cfg: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int],
                    dtype=torch.float32, order: Optional[List[tuple]] = None,
-                   windows: Optional[Dict[int, int]] = None) -> torch.Tensor:
-    """Logits [L, V] of every position of one whole sequence.
+                   windows: Optional[Dict[int, int]] = None, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [L, V] of every position of one whole sequence (or of the positions ``rows`` alone: the head of
+    a large vocabulary is most of the work, and a test that looks at a few positions need not pay for all).
 
     ``order`` is an optional list of (layer index, index in ``order`` of the call
     whose keys/values are read, or None); the default runs layers 0..L-1 once,
@@ -179,7 +180,7 @@ def forward_logits(cfg: dict, weights: Dict[str, torch.Tensor], ids: Sequence[in
 
     crates/prelude-core/src/models/qwen3.rs:601-623 (backbone), 637-673 (head)
     """
-    w = {k: v.to(dtype) for k, v in weights.items()}
+    w = weights if all(v.dtype == dtype for v in weights.values()) else {k: v.to(dtype) for k, v in weights.items()}
     ids_t = torch.as_tensor(list(ids), dtype=torch.long)
     L = ids_t.numel()
     cos, sin = rope_tables(cfg["head_dim"], L, cfg["rope_theta"], dtype)
@@ -192,6 +193,8 @@ def forward_logits(cfg: dict, weights: Dict[str, torch.Tensor], ids: Sequence[in
         win = None if windows is None else windows.get(n)
         res, kv = decoder_block(res, w, layer, cfg, cos, sin, kv_from, win)
         kvs.append(kv)
+    if rows is not None:
+        res = res[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rms_norm(res, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return x @ head.T

@@ -176,3 +176,51 @@ def test_random_orders_keep_the_books(seed, window):
         m.release(rid)
     m.check()
     assert all(g.allocator.num_free == 24 for g in m.groups) and m.slots.num_free == 5
+
+
+def test_device_table_updates_write_every_cell_once_and_follow_the_host_tables():
+    """The writes queued for the device-resident block tables: applied flush by flush (at random moments, so that
+    requests end, start over and get their slot used again between two flushes), a mirror of the device tables
+    agrees with the host tables of every live request, and no flush holds a cell twice (the scatter kernel
+    writes its entries side by side, so a second entry for a cell would race with the first)."""
+    import numpy as np
+    rng = random.Random(7)
+    page, slots, width_tokens = 4, 3, 64
+    needs = [KvPagesNeed(2, 16), KvPagesNeed(2, 16, 8)]            # all keys; a window of them (pages are trimmed)
+    m = CacheManager(needs, page, 40, slots, device=None, max_request_tokens=width_tokens)
+    assert m.table_width == width_tokens // page and not m.device_tables
+    mirror = {g.gid: np.full((slots, m.table_width), -1, np.int64) for g in m.groups}
+
+    def flush():
+        for gid, arr in m.take_table_updates().items():
+            assert len(set(arr[0].tolist())) == arr.shape[1], "a cell is written twice in one flush"
+            mirror[gid].reshape(-1)[arr[0]] = arr[1]
+        for rc in m.requests.values():
+            for gid, table in rc.tables.items():
+                assert mirror[gid][rc.slot, :len(table)].tolist() == table
+
+    live, next_id = {}, 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.3 and len(live) < slots:
+            m.add_request(next_id)
+            live[next_id] = 0
+            next_id += 1
+        elif op < 0.75 and live:
+            rid = rng.choice(list(live))
+            n = min(width_tokens, live[rid] + rng.randint(1, 9))
+            m.grow(rid, n)
+            live[rid] = n
+            m.trim(rid)
+        elif op < 0.85 and live:
+            rid = rng.choice(list(live))
+            m.reset_request(rid)                                       # starts over in the same slot
+            live[rid] = 0
+        elif live:
+            rid = rng.choice(list(live))
+            m.release(rid)                                             # its slot goes to whoever comes next
+            del live[rid]
+        if rng.random() < 0.3:
+            flush()
+        m.check()
+    flush()

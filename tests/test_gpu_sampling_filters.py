@@ -1,7 +1,4 @@
-"""NOT COLLECTED YET (the file name keeps pytest away): it has not run on a GPU so far; rename it to
-test_z_gpu_sampling_filters.py after its first green run on a B200.
-
-Top-k and top-p through the entry point (the reference's host route: softmax on the device, filter and draw on
+"""Top-k and top-p through the entry point (the reference's host route: softmax on the device, filter and draw on
 the host): every drawn token lies inside the set that the plain implementation's logits allow, a request's tokens
 follow from its seed alone, and the captured decode step and the launched one draw the same tokens."""
 import numpy as np
@@ -75,3 +72,61 @@ def test_drawn_tokens_lie_inside_the_filtered_set(folder, top_k, top_p):
     eng = _engine(folder)
     other = eng.generate(prompts, temperature=T, top_k=top_k, top_p=top_p, seed=12, max_new_tokens=new, ignore_eos=True)
     assert [r.token_ids for r in other] != outs[True]
+
+
+def _philox_uniform(seed, counter):
+    """Philox4x32-10 restated in Python (Salmon et al. 2011): the number the sampler draws for (seed, counter)."""
+    M0, M1, W0, W1, mask = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85, 0xFFFFFFFF
+    c = [counter & mask, (counter >> 32) & mask, 0, 0]
+    k0, k1 = seed & mask, (seed >> 32) & mask
+    for _ in range(10):
+        p0, p1 = M0 * c[0], M1 * c[2]
+        c = [((p1 >> 32) ^ c[1] ^ k0) & mask, p1 & mask, ((p0 >> 32) ^ c[3] ^ k1) & mask, p0 & mask]
+        k0, k1 = (k0 + W0) & mask, (k1 + W1) & mask
+    return (c[0] >> 8) / 16777216.0
+
+
+def _check_inverse_cdf(cfg, w, prompt, tokens, temperature, seed):
+    """Token i of a request is the first index whose cumulative probability, in index order, exceeds
+    philox(seed, i): over the plain implementation's softmax in float64, teacher-forced on the engine's tokens.
+    Where the draw lands within rounding of a boundary, the neighbour is accepted."""
+    logits = forward_logits(cfg, w, prompt + tokens, dtype=torch.float64)
+    exact = 0
+    for i, tok in enumerate(tokens):
+        row = logits[len(prompt) - 1 + i]
+        p = torch.exp((row - row.max()) / temperature)
+        cum = torch.cumsum(p, 0)
+        total = float(cum[-1])
+        target = _philox_uniform(seed, i) * total
+        want = int(torch.searchsorted(cum, torch.tensor(target, dtype=torch.float64), right=True))
+        lo = float(cum[tok - 1]) if tok > 0 else 0.0
+        hi = float(cum[tok])
+        assert tok == want or abs(target - lo) < 1e-4 * total or abs(target - hi) < 1e-4 * total, \
+            f"token {i}: drew {tok}, the seed's draw {target / total:.6f} falls on {want}"
+        exact += tok == want
+    return exact
+
+
+@pytest.mark.parametrize("mode", ["launched", "graphs", "bursts", "preempted"])
+def test_a_sampled_token_is_the_draw_of_its_seed_and_its_count(folder, mode):
+    """Seed and count reach the kernel as they should through launched steps, captured steps, queued runs of
+    captured steps, and across a preemption (the count goes on from the tokens already generated)."""
+    cfg, w = tiny.PARAMS["B"][0], tiny.read_weights(folder)
+    prompts = [tiny.random_ids(n, cfg["vocab_size"], 300 + n) for n in (6, 21, 11, 14)]
+    seeds = [11, 2**40 + 5, 7, 11]
+    T, new = 0.9, 18
+    from prelude_b200 import SamplingParams
+    sp = [SamplingParams(temperature=T, seed=s, max_new_tokens=new, ignore_eos=True) for s in seeds]
+    kw = {"launched": dict(cuda_graph=False), "graphs": dict(decode_burst=1), "bursts": dict(decode_burst=6),
+          "preempted": dict(decode_burst=1, num_pages=11, decode_reservation_cap=1)}[mode]
+    eng = _engine(folder, **kw)
+    res = eng.generate(prompts, sp)
+    assert all(len(r.token_ids) == new for r in res)
+    if mode == "preempted":
+        assert sum(r.preemptions for r in res) >= 1
+    if mode in ("graphs", "bursts"):
+        assert eng.stats().graph_steps > 0
+    exact = sum(_check_inverse_cdf(cfg, w, p, r.token_ids, T, s) for p, r, s in zip(prompts, res, seeds))
+    assert exact >= len(prompts) * new - 2                     # boundary cases are rare
+    eng.cache.check()
+    assert eng.cache.used_pages() == 0
