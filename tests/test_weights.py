@@ -139,3 +139,42 @@ def test_random_folder_is_seeded_and_by_role(tmp_path):
     with pytest.raises(Exception):
         write_random_model(str(tmp_path / "bad"), dict(tiny.TINY_A, head_dim=7))
     assert not os.path.exists(str(tmp_path / "bad" / "model.safetensors"))
+
+
+def test_tensors_an_architecture_names_as_ignored_are_passed_over():
+    """A checkpoint may carry buffers the parts never read; an architecture lists their name patterns in its model
+    spec and the check passes over them (the reference ignores every extra tensor; here the rest still count)."""
+    from dataclasses import replace
+    from prelude_b200.config import load_model_config
+    from prelude_b200.parts.model import DecoderModel
+    spec = load_model_config(tiny.TINY_A).to_model_spec()
+    tensors = dict(random_tensors(tiny.TINY_A, seed=0))
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    tensors["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    store = WeightStore.from_tensors(tensors)
+    req, opt = DecoderModel(spec).tensors()
+    with pytest.raises(WeightError) as e:
+        store.check(req, opt, spec.ignored_tensors)
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq", "model.layers.1.self_attn.rotary_emb.inv_freq"]
+    lenient = replace(spec, ignored_tensors=("*.rotary_emb.inv_freq",))
+    store.check(req, opt, lenient.ignored_tensors)
+    tensors["model.extra.weight"] = torch.zeros(3)
+    with pytest.raises(WeightError) as e:
+        WeightStore.from_tensors(tensors).check(req, opt, lenient.ignored_tensors)
+    assert e.value.unexpected == ["model.extra.weight"]
+
+
+def test_the_two_ends_of_the_model_are_parts():
+    from prelude_b200.config import load_model_config
+    from prelude_b200.config.spec import LinearHeadSpec, TokenEmbeddingSpec
+    from prelude_b200.parts.model import DecoderModel
+    from prelude_b200.parts.registry import FAMILIES, part_class
+    assert "embedding" in FAMILIES and "head" in FAMILIES
+    for cfg, tied in ((tiny.TINY_A, True), (tiny.TINY_B, False)):
+        spec = load_model_config(cfg).to_model_spec()
+        assert spec.embedding_spec() == TokenEmbeddingSpec(cfg["vocab_size"], cfg["hidden_size"])
+        assert spec.head_spec() == LinearHeadSpec(cfg["vocab_size"], cfg["hidden_size"], tied)
+        m = DecoderModel(spec)
+        assert isinstance(m.embedding, part_class("embedding", "token_embedding"))
+        req, opt = m.tensors()
+        assert ("lm_head.weight" in opt) == tied and ("lm_head.weight" in req) == (not tied)
