@@ -22,6 +22,9 @@ extern "C" {
  *  - The first call on a device looks up the array's device address; make it before a stream capture begins.
  *  - Every call uses the same array, which keeps the previous call's contents.  Nothing needs to start at zero.
  *    Calls that overlap on the GPU (different streams or threads) race on it; calls on one stream do not.
+ *  - The array that a call uses is the one of the device that is current when it is made.  logits, out and
+ *    `stream` must belong to that device: make it current (cudaSetDevice) before the call.  Logits on another
+ *    device are refused.
  *  - logits, out: device pointers; the launch goes to `stream`; nothing is synchronised.
  * Returns 0 on success. */
 int pb_argmax_noalloc(const float* logits, long long row_stride, int rows, int vocab, int32_t* out,

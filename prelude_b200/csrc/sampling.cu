@@ -18,6 +18,7 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <mutex>
 
 #define SAMP_THREADS 1024
 #define PART_THREADS 256
@@ -310,13 +311,26 @@ PB_API int pb_argmax_noalloc(const float* logits, long long row_stride, int rows
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return pb_fail("argmax_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
     PB_REQUIRE(dev >= 0 && dev < PB_NOALLOC_MAX_DEVICES, "argmax_noalloc: device %d", dev);
-    if (g_noalloc_scratch_addr[dev] == nullptr) {
-        // the array's name is a host-side handle here, not a device address: ask the runtime for the address
-        float* addr = nullptr;
-        e = cudaGetSymbolAddress((void**)&addr, g_noalloc_scratch);
-        if (e != cudaSuccess || addr == nullptr)
-            return pb_fail("argmax_noalloc: cannot find the built-in scratch on device %d: %s", dev, cudaGetErrorString(e));
-        g_noalloc_scratch_addr[dev] = addr;
+    // The array that is used is the CURRENT device's.  The logits must live there too (and the stream must be one
+    // of that device's, which the runtime checks at the launch): another device's array is not this call's to use.
+    cudaPointerAttributes where;
+    e = cudaPointerGetAttributes(&where, logits);
+    if (e != cudaSuccess) return pb_fail("argmax_noalloc: cannot tell where the logits live: %s", cudaGetErrorString(e));
+    PB_REQUIRE(where.type != cudaMemoryTypeDevice || where.device == dev,
+               "argmax_noalloc: the logits live on device %d, the current device is %d; make the logits' device current first",
+               where.device, dev);
+    {
+        // the first call on a device resolves the address; a lock keeps two threads' first calls apart
+        static std::mutex first_call;
+        std::lock_guard<std::mutex> hold(first_call);
+        if (g_noalloc_scratch_addr[dev] == nullptr) {
+            // the array's name is a host-side handle here, not a device address: ask the runtime for the address
+            float* addr = nullptr;
+            e = cudaGetSymbolAddress((void**)&addr, g_noalloc_scratch);
+            if (e != cudaSuccess || addr == nullptr)
+                return pb_fail("argmax_noalloc: cannot find the built-in scratch on device %d: %s", dev, cudaGetErrorString(e));
+            g_noalloc_scratch_addr[dev] = addr;
+        }
     }
     launch_two_pass(logits, row_stride, rows, vocab, nullptr, nullptr, nullptr, g_noalloc_scratch_addr[dev], out, stream);
     PB_CHECK_LAUNCH("argmax_noalloc");

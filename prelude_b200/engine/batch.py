@@ -86,6 +86,7 @@ class StepBatch:
     decode_only: bool = False
     extras: Dict[str, object] = field(default_factory=dict)    # per-kernel plans made once per step
     real_tokens: int = -1               # tokens that exist; a captured step is padded to n_tokens (-1: all exist)
+    h2d_bytes: int = 0                  # bytes of the host-to-device copy that brought this step's inputs
 
     @property
     def table_row_of_token(self) -> torch.Tensor:
@@ -182,4 +183,5 @@ def build_step_batch(items: Sequence[StepItem], block_tables: Dict[int, List[Lis
         n_tokens=T, n_seqs=R, token_ids=cut(0), positions=cut(1), token_seq=cut(2), cu_q=cut(3), q_start=cut(4),
         kv_len=cut(5), state_slots=cut(6), logit_rows=cut(7), block_tables=tables_dev, status=dev[-1:],
         q_lens=q_lens, q_start_host=q_start, kv_len_host=kv_len, state_slots_host=slots,
-        max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()))
+        max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()),
+        h2d_bytes=flat.numel() * 4)

@@ -57,6 +57,8 @@ class EngineStats:
     pages_total: int = 0
     pages_in_use_peak: int = 0
     step_ms_total: float = 0.0
+    h2d_bytes: int = 0                  # bytes copied host to device for the steps' inputs (counted from the tensors copied)
+    d2h_bytes: int = 0                  # bytes read back: sampled tokens and the status word
 
 
 def _activation_reserve_bytes(model: DecoderModel, max_tokens: int, max_rows: int) -> int:
@@ -410,7 +412,7 @@ class Engine:
         starts = self.runner.reserve(entries)
         for it in items:
             self.cache.grow(it.seq.request_id, it.start + k)
-        self.cache.flush_table_updates()
+        flushed = self.cache.flush_table_updates()
         self.cache.zero_fresh_state()
         g = self.burst_graphs.get(len(items))
         g.load([e.tokens[0] for e in entries], starts, [self.cache.slot_of(e.request_id) for e in entries],
@@ -428,6 +430,8 @@ class Engine:
         for e in entries:
             self.cache.trim(e.request_id)
         st = self._stats
+        st.h2d_bytes += g.h2d_bytes + 8 * flushed          # one load for the whole run
+        st.d2h_bytes += 4 * (k * len(items) + 1)
         st.graph_steps += k
         st.steps += k
         st.decode_steps += k
@@ -455,9 +459,11 @@ class Engine:
                 and self.graphs.usable(len(items), max(it.start + 1 for it in items))):
             # the captured step: same reservation, same kernels, fixed buffers
             starts = self.runner.reserve(entries)
-            self.cache.flush_table_updates()
+            flushed = self.cache.flush_table_updates()
             self.cache.zero_fresh_state()
             g = self.graphs.get(len(items))
+            st.h2d_bytes += g.h2d_bytes + 8 * flushed
+            st.d2h_bytes += g.d2h_bytes
             g.load([e.tokens[0] for e in entries], starts, [self.cache.slot_of(e.request_id) for e in entries],
                    temps, seeds, counters)
             g.replay()
@@ -471,6 +477,8 @@ class Engine:
             logits = self.runner.step(entries, check_status=False)
             sampled = self.sampler.sample(logits, temps, top_ks, top_ps, seeds, counters) if rows else []
             raise_on_status(int(self.runner.last_batch.status.item()))
+            st.h2d_bytes += self.runner.last_batch.h2d_bytes
+            st.d2h_bytes += 4 * (len(rows) + 1)
         st.steps += 1
         st.decode_steps += 1 if decode_only else 0
         st.generated_tokens += len(rows)

@@ -130,7 +130,7 @@ class StepGraph:
         keep = {k: val for k, val in b.extras.items() if k == "recorder" or (isinstance(k, tuple) and k and k[0] == "workspace")}
         b.extras.clear()
         b.extras.update(keep)                              # the plans of the step before do not fit this one
-        b.n_seqs, b.real_tokens = R, T
+        b.n_seqs, b.real_tokens, b.h2d_bytes = R, T, self.host.numel() * 4
         b.logit_rows = self._logit_rows[:len(rows)]
         b.q_lens, b.q_start_host, b.kv_len_host, b.state_slots_host = q_lens, q_start, kv_len, slots
         b.max_q_len, b.max_kv_len, b.decode_only = int(q_lens.max()), int(kv_len.max()), False

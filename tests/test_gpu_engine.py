@@ -168,3 +168,42 @@ def test_the_first_tokens_of_a_sequence(folders, which, dtype):
     _compare(got, ref, dtype)
     runner.cache.check()
     assert runner.cache.used_pages() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which", ["D", "E"])
+def test_long_portions_behind_a_cached_prefix(folders, which, dtype):
+    """Portions of 64 to 130 tokens that continue a cached prefix, alone and beside single decoded tokens of other
+    requests: long enough for the tcgen05 prompt-attention kernel (where it takes the shape) to start in the
+    middle of a request, with captured prompt steps on as in the entry point."""
+    folder = folders[(which, dtype)]
+    cfg, _, page = tiny.PARAMS[which]
+    reqs = {"p": tiny.random_ids(330, cfg["vocab_size"], 31), "q": tiny.random_ids(200, cfg["vocab_size"], 32),
+            "r": tiny.random_ids(90, cfg["vocab_size"], 33)}
+    ref = _reference(which, folder, reqs)
+    alone = harness.portions(reqs, sizes=(30, 70, 2, 130, 64, 3, 1))
+    # mixed by hand: p's long portions beside q's and r's single tokens
+    beside, fed = [], {"p": 0, "q": 0, "r": 0}
+    beside.append(([("q", reqs["q"][:150], list(range(150))), ("r", reqs["r"][:60], list(range(60)))], []))
+    fed["q"], fed["r"] = 150, 60
+    for n in (33, 64, 100, 128, 5):
+        entries = [("p", reqs["p"][fed["p"]:fed["p"] + n], list(range(n)))]
+        fed["p"] += n
+        for rid in ("q", "r"):
+            if fed[rid] < len(reqs[rid]):
+                entries.append((rid, reqs[rid][fed[rid]:fed[rid] + 1], [0]))
+                fed[rid] += 1
+        beside.append((entries, []))
+    beside.append(([(rid, reqs[rid][fed[rid]:], list(range(len(reqs[rid]) - fed[rid]))) for rid in reqs
+                    if fed[rid] < len(reqs[rid])], list(reqs)))
+    for schedule in (alone, beside):
+        from prelude_b200.engine.loading import load_model, make_runner
+        model = load_model(folder, dtype, "cuda:0")
+        runner = make_runner(model, page_size=page, num_pages=harness.peak_tokens(schedule, page) // page, max_slots=8,
+                             max_request_tokens=512)
+        runner.enable_step_graphs()
+        got = harness.run_schedule(runner, schedule)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        _compare(got, ref, dtype)
+        runner.cache.check()
+        assert runner.cache.used_pages() == 0
