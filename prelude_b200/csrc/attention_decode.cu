@@ -34,11 +34,18 @@
 //    scores, running maximum and sum in float32, probabilities rounded to
 //    bfloat16 for the second product.  No block-wide barrier in the loop.  The
 //    warps are merged through shared memory at the end.
-//  * With more than one split, every block writes its unnormalised partial
-//    result with its maximum and sum to scratch memory and counts itself in;
-//    the block that arrives last for a (token, key/value head) adds the splits
-//    up in ascending order and writes the output.  The counters are left at
-//    zero for the next call.
+//  * With more than one split, the blocks of a (token, key/value head) are
+//    launched as one thread-block cluster where the device can place it (up to
+//    16 blocks): every block leaves its unnormalised partial result with its
+//    maximum and sum in its own shared memory, the cluster meets at its
+//    barrier, and every block adds up a slice of the output elements over all
+//    blocks, in ascending order, reading the others' parts through distributed
+//    shared memory.  No scratch memory, no fence, no counter, no reload: the
+//    end of the kernel is two cluster barriers and one remote read.
+//  * Splits that do not fit a cluster go through scratch memory: every block
+//    writes its part there and counts itself in; the block that arrives last
+//    adds the splits up in ascending order and writes the output.  The
+//    counters are left at zero for the next call.
 //  * All keys and values but the newest were written by earlier steps, so the
 //    loaders start the stream before the kernel that precedes this one on the
 //    stream (it writes q and the newest key and value) has finished, and wait
@@ -48,13 +55,20 @@
 //    step's status word and goes on to the end.
 #include "attention_common.cuh"
 
+#include <stdlib.h>
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
 #define DEC_LOADERS 128         // threads of the lsu path's four loader warps
+#define DEC_MAX_CLUSTER 16      // blocks of one (token, key/value head) that may form a thread-block cluster
 #define DEC_MAX_PAGES 512       // page ids of one block's share kept in shared memory (else read from the table)
 
 struct DecodeParams {
     AttnParams a;
     int* counters;              // [n_tokens * n_kv_heads], zero on entry and on exit
     int page_shift;             // log2(page_size) when it is a power of two, else -1
+    int cluster;                // the blocks of a (token, key/value head) are one thread-block cluster: they add
+                                // their parts up through each other's shared memory instead of scratch memory
 };
 
 #define BNW 64                  // keys per consumer tile
@@ -283,6 +297,8 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
     float* sO = reinterpret_cast<float*>(stages);           // [4][16][DMAX]
     float* sM = sO + 4 * 16 * DMAX;                         // [4][16]
     float* sL = sM + 64;
+    float* sC = sL + 64 + 2 * 16 * 64 + 16;                 // [16][DMAX] this block's part, for the cluster's other blocks
+    float* sCml = sC + 16 * DMAX;                           // [16][2] its maxima and sums
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
@@ -314,6 +330,9 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
         const size_t th = (size_t)tok * p.n_heads + kvh * G + row;
         if (p.n_splits == 1) {
             p.out[th * d + col] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
+        } else if (dp.cluster) {
+            sC[idx] = acc;                                  // this block's part stays in its shared memory
+            if (col == 0) { sCml[row * 2] = mm; sCml[row * 2 + 1] = ls; }
         } else {
             p.part_o[(th * p.n_splits + split) * d + col] = acc;
             if (col == 0) {
@@ -323,6 +342,43 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
         }
     }
     if (p.n_splits == 1) return;
+    if (dp.cluster) {
+        // The cluster is the (token, key/value head)'s splits, in order: block rank = split.  After the barrier every
+        // block's part is in place; block r adds up the r-th slice of the output elements over all parts, in
+        // ascending order, and the second barrier keeps every block's shared memory alive until all have read it.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int ns = p.n_splits, rank = (int)cluster.block_rank();
+        const int per = (G * d + ns - 1) / ns;
+        const size_t th0 = (size_t)tok * p.n_heads + kvh * G;
+        for (int idx = rank * per + threadIdx.x; idx < min(G * d, (rank + 1) * per); idx += DEC_THREADS) {
+            const int row = idx / d;
+            float ms[16], lsum[16], part[16];
+            float mm = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 16; ++sp) {
+                if (sp < ns) {
+                    const float* rml = cluster.map_shared_rank(sCml, sp);
+                    ms[sp] = rml[row * 2];
+                    lsum[sp] = rml[row * 2 + 1];
+                    part[sp] = cluster.map_shared_rank(sC, sp)[idx];
+                    mm = fmaxf(mm, ms[sp]);
+                }
+            }
+            float acc = 0.f, ls = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 16; ++sp) {
+                if (sp < ns) {
+                    const float f = (ms[sp] == -INFINITY) ? 0.f : exp2f(ms[sp] - mm);
+                    ls += f * lsum[sp];
+                    acc += f * part[sp];
+                }
+            }
+            p.out[th0 * d + idx] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
+        }
+        cluster.sync();
+        return;
+    }
     // count this split in; the last one adds all splits up, in ascending order
     __threadfence();
     __syncthreads();
@@ -423,13 +479,12 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
 template <int DMAX, bool BULK, bool PAIR> static size_t decode_smem() {
     using T = DecodeTiling<DMAX, BULK, PAIR>;
     size_t tiles = (size_t)T::STAGES * T::STAGE_ELEMS * 2 + (size_t)16 * (DMAX + 8) * 2 + DEC_MAX_PAGES * 4;
-    size_t merge = (size_t)(4 * 16 * DMAX + 128 + 2 * 16 * 64 + 16) * 4;   // the warps' partial results, then the splits' maxima and sums
+    // the warps' partial results, the splits' maxima and sums, this block's part for its cluster
+    size_t merge = (size_t)(4 * 16 * DMAX + 128 + 2 * 16 * 64 + 16 + 16 * DMAX + 32) * 4;
     return tiles > merge ? tiles : merge;
 }
 
-template <int DMAX, bool BULK, bool PAIR>
-static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
-    using T = DecodeTiling<DMAX, BULK, PAIR>;
+template <int DMAX, bool BULK, bool PAIR> static int decode_configure() {
     static bool configured = false;
     size_t smem = decode_smem<DMAX, BULK, PAIR>();
     if (!configured) {
@@ -437,7 +492,66 @@ static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
         if (e != cudaSuccess) return pb_fail("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    pb_launch(attn_decode_kernel<DMAX, BULK, PAIR>, dim3(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens), dim3(T::THREADS), smem, stream, dp);
+    return 0;
+}
+
+// How many clusters of `ns` blocks of this kernel the device holds at a time (0: it cannot place one); asked once per size.
+template <int DMAX, bool BULK, bool PAIR> static int decode_clusters_resident(int ns) {
+    using T = DecodeTiling<DMAX, BULK, PAIR>;
+    static int known[DEC_MAX_CLUSTER + 1];
+    static bool asked[DEC_MAX_CLUSTER + 1] = {false};
+    if (ns < 2 || ns > DEC_MAX_CLUSTER) return 0;
+    if (!asked[ns]) {
+        asked[ns] = true;
+        known[ns] = 0;
+        if (decode_configure<DMAX, BULK, PAIR>() != 0) return 0;
+        cudaError_t e = cudaSuccess;
+        if (ns > 8) e = cudaFuncSetAttribute(attn_decode_kernel<DMAX, BULK, PAIR>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(ns * 4096, 1, 1);
+            cfg.blockDim = dim3(T::THREADS);
+            cfg.dynamicSmemBytes = decode_smem<DMAX, BULK, PAIR>();
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = ns; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            e = cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<DMAX, BULK, PAIR>, &cfg);
+            if (e == cudaSuccess && n > 0) known[ns] = n;
+        }
+        (void)cudaGetLastError();
+    }
+    return known[ns];
+}
+
+template <int DMAX, bool BULK, bool PAIR>
+static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
+    using T = DecodeTiling<DMAX, BULK, PAIR>;
+    size_t smem = decode_smem<DMAX, BULK, PAIR>();
+    if (int e = decode_configure<DMAX, BULK, PAIR>()) return e;
+    const dim3 grid(dp.a.n_splits, dp.a.n_kv_heads, dp.a.n_tokens);
+    DecodeParams q = dp;
+    const int ns = dp.a.n_splits;
+    q.cluster = (dp.cluster && decode_clusters_resident<DMAX, BULK, PAIR>(ns) > 0) ? 1 : 0;
+    if (q.cluster) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(T::THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = ns; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pb_pdl_enabled() ? 2 : 1;
+        cudaLaunchKernelEx(&cfg, attn_decode_kernel<DMAX, BULK, PAIR>, q);
+    } else {
+        pb_launch(attn_decode_kernel<DMAX, BULK, PAIR>, grid, dim3(T::THREADS), smem, stream, q);
+    }
     return 0;
 }
 
@@ -460,12 +574,76 @@ PB_API int pb_attention_decode_blocks_per_sm(int head_dim) {
     return n < 1 ? 1 : n;
 }
 
+// Whether the splits of a (token, key/value head) are launched as a thread-block cluster: yes unless
+// PRELUDE_DECODE_CLUSTER=0 or pb_attention_decode_set_cluster(0) says otherwise.
+static int g_dec_clusters = -1;
+static int dec_use_clusters() {
+    if (g_dec_clusters < 0) {
+        const char* off = getenv("PRELUDE_DECODE_CLUSTER");
+        g_dec_clusters = (off && off[0] == '0') ? 0 : 1;
+    }
+    return g_dec_clusters;
+}
+PB_API void pb_attention_decode_set_cluster(int on) { g_dec_clusters = on ? 1 : 0; }
+
+// The most splits whose blocks can add their parts up as one thread-block cluster (more go through scratch memory).
+PB_API int pb_attention_decode_cluster_max() { return dec_use_clusters() ? DEC_MAX_CLUSTER : 0; }
+
 // Scratch floats a call needs for its splits: (head_dim + 2) per token, head and split.
 PB_API long long pb_attention_decode_scratch_floats(int n_tokens, int n_heads, int head_dim, int n_splits) {
     if (n_splits <= 1) return 0;
     return (long long)n_tokens * n_heads * n_splits * (head_dim + 2);
 }
 
+static bool dec_bulk(int head_dim, int page_size, int swizzle) {
+    // bulk copies bring whole runs of a page: a run must tile the 64-key tile evenly and start at a multiple
+    // of 8 tokens (the rows then sit at the row numbers their permutation was made for)
+    return swizzle && page_size % 8 == 0 && (BNW % page_size == 0 || page_size % BNW == 0) &&
+           (head_dim == 64 || head_dim == 128 || head_dim == 256);    // the dense layout has no room for a narrower head
+}
+
+// Into how many parts a decode step cuts the keys of every (token, key/value head), for contexts of up to
+// max_context keys, and whether the parts are added up inside a thread-block cluster (the return value is the
+// count, plus 256 when they are).  Every candidate is rated by what its busiest multiprocessor has to stream, in
+// 64-key tiles, plus what adding the parts up costs (measured on B200: about three tiles' time inside a cluster,
+// about seven through scratch memory, a tile taking 0.6 us).  Candidates: no cut; 2 to 8 parts as a cluster, but
+// only where the device holds the clusters of all pairs at one time (a cluster needs its blocks on one processor
+// group, and a second round of clusters would wait for the first; the driver says how many fit); and, through
+// scratch memory, as many parts as the device holds blocks at a time (never more than there are tiles, or 64).
+PB_API int pb_attention_decode_plan(int n_tokens, int n_kv_heads, int head_dim, int page_size, int swizzle, int max_context) {
+    const int sms = dec_sms();
+    const long long pairs = (long long)(n_tokens < 1 ? 1 : n_tokens) * (n_kv_heads < 1 ? 1 : n_kv_heads);
+    const int tiles = max_context < 1 ? 1 : (max_context + 63) / 64;
+    const bool bulk = dec_bulk(head_dim, page_size, swizzle);
+    const int dmax = head_dim <= 64 ? 64 : head_dim <= 128 ? 128 : 256;
+    long long most = (long long)sms * pb_attention_decode_blocks_per_sm(head_dim) / pairs;
+    if (most > tiles) most = tiles;
+    if (most > 64) most = 64;
+    if (most < 1) most = 1;
+    if (pairs > 65536) return 1;
+    auto load = [&](long long s) { return (double)((pairs * s + sms - 1) / sms) * ((double)tiles / (double)s); };
+    int best = 1;
+    double best_cost = load(1);
+    if (most > 1 && load(most) + 7.0 < best_cost) { best = (int)most; best_cost = load(most) + 7.0; }
+    if (dec_use_clusters()) {
+        for (int s = 2; s <= 8 && s <= tiles; ++s) {
+            const bool pair = bulk && head_dim <= 128 && pairs * s > sms;
+            int held = 0;
+            if (dmax == 64) held = bulk ? (pair ? decode_clusters_resident<64, true, true>(s) : decode_clusters_resident<64, true, false>(s))
+                                        : decode_clusters_resident<64, false, false>(s);
+            else if (dmax == 128) held = bulk ? (pair ? decode_clusters_resident<128, true, true>(s) : decode_clusters_resident<128, true, false>(s))
+                                              : decode_clusters_resident<128, false, false>(s);
+            else held = bulk ? decode_clusters_resident<256, true, false>(s) : decode_clusters_resident<256, false, false>(s);
+            if (held < pairs) continue;
+            const double cost = load(s) + 3.0;
+            if (cost <= best_cost) { best = s | 256; best_cost = cost; }
+        }
+    }
+    return best;
+}
+
+// cluster: add the splits' parts up inside a thread-block cluster where the device can place one of n_splits blocks
+// (up to 16), else through scratch memory.
 // scratch: pb_attention_decode_scratch_floats(...) floats, or null when n_splits == 1.
 // counters: n_tokens * n_kv_heads ints, zero before the first call; every call leaves them
 // zero, so calls that follow one another on a stream may share them.  Null when n_splits == 1.
@@ -473,7 +651,7 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
                                     const int32_t* block_table, int table_stride, const int32_t* positions,
                                     const int32_t* token_seq, int page_size, int num_pages, int n_tokens,
                                     int n_heads, int n_kv_heads, int head_dim, float scale, int window, int swizzle,
-                                    int n_splits, float* scratch, int* counters, int* status, cudaStream_t stream) {
+                                    int n_splits, int cluster, float* scratch, int* counters, int* status, cudaStream_t stream) {
     DecodeParams dp{};
     AttnParams& p = dp.a;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
@@ -487,6 +665,7 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
     PB_REQUIRE(p.group <= 16, "attention_decode: %d query heads per key/value head; at most 16 fit a tile", p.group);
     PB_REQUIRE(n_splits >= 1 && n_splits <= 1024, "attention_decode: n_splits=%d", n_splits);
     PB_REQUIRE(n_tokens < 65536 && n_kv_heads < 65536, "attention_decode: bad grid");
+    dp.cluster = (cluster && dec_use_clusters() && n_splits > 1 && n_splits <= DEC_MAX_CLUSTER) ? 1 : 0;
     PB_REQUIRE(n_splits == 1 || (scratch != nullptr && counters != nullptr),
                "attention_decode: %d splits need scratch memory and counters", n_splits);
     if (n_tokens == 0) return 0;
@@ -498,10 +677,7 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
     dp.page_shift = -1;
     for (int s = 0; s < 31; ++s)
         if ((1 << s) == page_size) dp.page_shift = s;
-    // bulk copies bring whole runs of a page: a run must tile the 64-key tile evenly and start at a multiple
-    // of 8 tokens (the rows then sit at the row numbers their permutation was made for)
-    const bool bulk = swizzle && page_size % 8 == 0 && (BNW % page_size == 0 || page_size % BNW == 0) &&
-                      (head_dim == 64 || head_dim == 128 || head_dim == 256);    // the dense layout has no room for a narrower head
+    const bool bulk = dec_bulk(head_dim, page_size, swizzle);
     // more blocks than multiprocessors: two per multiprocessor with half the ring each
     const bool pair = bulk && head_dim <= 128 && (long long)n_tokens * n_kv_heads * n_splits > dec_sms();
     int e = pair ? (head_dim == 64 ? launch_decode<64, true, true>(dp, stream) : launch_decode<128, true, true>(dp, stream))
@@ -513,3 +689,4 @@ PB_API int pb_attention_decode_bf16(const void* q, const void* k_pages, const vo
     PB_CHECK_LAUNCH("attention_decode");
     return 0;
 }
+

@@ -50,13 +50,15 @@ def _decode_counters(device) -> torch.Tensor:
     return buf
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, head_dim: int, max_context: int, device) -> int:
-    """Over how many blocks a decode step spreads the keys of one (token, key/value head):
-    as many as the device holds at one time, never more than there are 64-key tiles."""
-    resident = _sm_count(device) * _l.library().pb_attention_decode_blocks_per_sm(head_dim)
-    blocks = max(1, n_tokens * n_kv_heads)
-    tiles = max(1, -(-max_context // 64))
-    return max(1, min(resident // blocks, tiles, 64))
+def decode_splits(n_tokens: int, n_kv_heads: int, head_dim: int, max_context: int, device, page_size: int = 16,
+                  swizzled: bool = True):
+    """(parts, cluster): over how many blocks a decode step spreads the keys of one (token, key/value head), and
+    whether those blocks add their parts up inside a thread-block cluster (through each other's shared memory)
+    or through scratch memory.  The library's plan: what fills the device, what the device holds as clusters at
+    one time, and what adding the parts up costs either way (``pb_attention_decode_plan``)."""
+    plan = int(_l.library().pb_attention_decode_plan(n_tokens, n_kv_heads, head_dim, page_size, 1 if swizzled else 0,
+                                                     max(1, int(max_context))))
+    return plan & 255, bool(plan & 256)
 
 
 def _prefill_plan(batch, tpt: int, min_len: int = 0, max_len: Optional[int] = None):
@@ -141,9 +143,11 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 
     def decode(t0: int, n: int, max_ctx: int) -> None:
         """Tokens t0 .. t0 + n of the batch, one per request, on the kernel that spreads a token's keys over blocks."""
+        row = nH * D * q.element_size()
         if window:
             max_ctx = min(max_ctx, window + 64)
-        splits = decode_splits(n, nKV, D, max_ctx, q.device)
+        plan = decode_splits(n, nKV, D, max_ctx, q.device, page_size, bool(swizzled))
+        splits, cluster = plan if isinstance(plan, tuple) else (int(plan), True)
         if n * nKV > (1 << 16):
             splits = 1
         # the partial results of the splits: one buffer per step and size, shared by the layers (a layer's attention
@@ -154,11 +158,10 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
             floats = lib.pb_attention_decode_scratch_floats(n, nH, D, splits)
             scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
             batch.extras[key] = scratch
-        row = nH * D * q.element_size()
         check(lib.pb_attention_decode_bf16(
             q.data_ptr() + t0 * row, k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr() + t0 * row, table.data_ptr(),
             table.shape[1], batch.positions.data_ptr() + 4 * t0, batch.table_row_of_token.data_ptr() + 4 * t0, page_size, num_pages,
-            n, nH, nKV, D, float(scale), win, swizzled, splits, scratch.data_ptr() if splits > 1 else None,
+            n, nH, nKV, D, float(scale), win, swizzled, splits, 1 if cluster else 0, scratch.data_ptr() if splits > 1 else None,
             _decode_counters(q.device).data_ptr() if splits > 1 else None, batch.status.data_ptr(), stream), "attention_decode")
 
     if batch.decode_only:

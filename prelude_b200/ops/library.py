@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 
 class KernelLibraryError(RuntimeError):
@@ -45,7 +45,10 @@ _SIGNATURES = {
     "pb_attention_prefill_tc_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
     "pb_attention_decode_scratch_floats": ([I, I, I, I], L),
     "pb_attention_decode_blocks_per_sm": ([I], I),
-    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P], I),
+    "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P], I),
+    "pb_attention_decode_cluster_max": ([], I),
+    "pb_attention_decode_plan": ([I, I, I, I, I, I], I),
+    "pb_attention_decode_set_cluster": ([I], None),
     "pb_gemm_stream_supported": ([I, I, I, L, L], I),
     "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, I, P, P], I),
     "pb_mlp_chain_counters": ([], I),

@@ -433,7 +433,7 @@ def _batch_for(requests, page, num_pages, nKV, D, seed, trimmed_below=None):
 
 def _check_dispatch(requests, nH, nKV, D, page, window, seed=0, trimmed_below=None, tolerance=None):
     from prelude_b200.ops.attention import paged_attention
-    batch, ks, vs, kp, vp = _batch_for(requests, page, 600, nKV, D, seed, trimmed_below)
+    batch, ks, vs, kp, vp = _batch_for(requests, page, max(600, sum(-(-c // page) for c, _ in requests) + 8), nKV, D, seed, trimmed_below)
     q = rnd(batch.n_tokens, nH, D, dtype=torch.bfloat16, seed=seed + 99)
     got = paged_attention(q, kp, vp, batch, 0, 1 / math.sqrt(D), window)
     assert int(batch.status.item()) == 0
@@ -510,13 +510,22 @@ def test_attention_prefill_tcgen05_refuses_what_it_does_not_take():
                                            (4, 2, 64, 24), (8, 2, 128, 48), (4, 1, 128, 64), (6, 3, 64, 128),
                                            (4, 4, 192, 16), (4, 1, 128, 8), (2, 2, 256, 40)])
 @pytest.mark.parametrize("window", [None, 70])
-@pytest.mark.parametrize("splits", [None, 1, 3, 8])
-def test_attention_decode_tensor_cores(monkeypatch, nH, nKV, D, page, window, splits):
+@pytest.mark.parametrize("splits,cluster", [(None, True), (1, True), (3, True), (8, True), (16, True), (None, False), (3, False), (20, True)],
+                         ids=["plan", "1", "3", "8", "16", "plan-scratch", "3-scratch", "20-scratch"])
+def test_attention_decode_tensor_cores(monkeypatch, nH, nKV, D, page, window, splits, cluster):
+    # the parts of a (token, head)'s splits are added up through the shared memory of a thread-block cluster (up to
+    # 16 splits, where the device places such a cluster) or through scratch memory (more splits, or clusters off)
     from prelude_b200.ops import attention
+    from prelude_b200.ops import library as L
     if splits is not None:
         monkeypatch.setattr(attention, "decode_splits", lambda *a, **k: splits)
     requests = [(1, 1), (2, 1), (63, 1), (64, 1), (65, 1), (128, 1), (129, 1), (500, 1), (777, 1)]
-    _check_dispatch(requests, nH, nKV, D, page, window)
+    L.library().pb_attention_decode_set_cluster(1 if cluster else 0)
+    try:
+        for _ in range(2):                                  # twice: the scratch way leaves its counters at zero
+            _check_dispatch(requests, nH, nKV, D, page, window)
+    finally:
+        L.library().pb_attention_decode_set_cluster(1)
 
 
 def test_attention_with_pages_that_a_window_has_given_back():

@@ -187,7 +187,7 @@ def test_captured_decode_steps_at_real_layer_sizes(batch):
     eng._run_step, eng._run_burst = watching_step, watching_burst
     res = eng.generate(prompts, temperature=0.0, max_new_tokens=new, ignore_eos=True)
     assert eng.stats().graph_steps >= new - 2 and len(seen) >= 2 * batch
-    splits = A.decode_splits(batch, 8, 128, 512, torch.device(DEV))
+    splits, _ = A.decode_splits(batch, 8, 128, 512, torch.device(DEV))
     assert splits > 1 or batch > 8, "the contexts must be long enough for the decode kernel to split the keys"
     w32 = s.weights(torch.float32)
     ids = {r.request_id: p + r.token_ids for p, r in zip(prompts, res)}
