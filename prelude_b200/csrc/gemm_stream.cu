@@ -39,11 +39,6 @@
 //    activation costs no kernel and the 2N-wide intermediate never exists.
 //  * Waits on barriers are bounded in time; a warp that gives up raises the
 //    status word and the block goes on to its end.
-// The tensor-memory kernel (gemm_tc.cu) is the wrong tool here: its instruction
-// takes 128 cycles for 128 rows however few columns it has, which is no faster
-// than memory delivers the weights, and its tiles are too coarse to give every
-// multiprocessor an equal share of a 2,560-row matrix without splitting K.
-//
 // The reference leaves these shapes to its GEMM libraries
 // (crates/prelude-cuda/src/ops/gemm.rs:35-137; DeepGEMM's small-M path).
 // Needs K % 16 == 0, 16-byte aligned rows of W and x, and x to fit in shared

@@ -202,14 +202,36 @@ __global__ void gather_add_rmsnorm_kernel(const TX* __restrict__ x, int n_parts,
         if (xr) for (int s = 0; s < n_parts; ++s) v += pb_ld(xr + s * part_stride + i);   // the parts in ascending order
         return v;
     };
+    // a thread's elements stay in registers between the two passes where the row is short enough (16 per thread:
+    // rows of up to 4,096 at 256 threads); the loads of the first pass are independent of one another
+    constexpr int KEEP = 16;
+    float kept[KEEP];
+    const bool fits = width <= KEEP * (int)blockDim.x;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = value(i);
-        ss += v * v;
+    if (fits) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            kept[k] = i < width ? value(i) : 0.f;
+            ss += kept[k] * kept[k];
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = value(i);
+            ss += v * v;
+        }
     }
     float total = block_sum(ss, red);
     float inv = 1.0f / sqrtf(total / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, value(i) * inv * w[i]);
+    if (fits) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < width) pb_st(out + i, kept[k] * inv * w[i]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, value(i) * inv * w[i]);
+    }
 }
 
 // x as for pb_add_rmsnorm: of type dtype, or x_parts float32 arrays to be added up.

@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 11
+ABI_VERSION = 12
 
 
 class KernelLibraryError(RuntimeError):
@@ -51,12 +51,6 @@ _SIGNATURES = {
     "pb_attention_decode_set_cluster": ([I], None),
     "pb_gemm_stream_supported": ([I, I, I, L, L], I),
     "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, I, P, P], I),
-    "pb_mlp_chain_counters": ([], I),
-    "pb_mlp_chain_supported": ([I, I, I, I, L, L, L], I),
-    "pb_mlp_chain_bf16": ([P, L, P, L, P, L, P, P, I, I, I, I, P, P, P], I),
-    "pb_gemm_tc_supported": ([I, I, I, L, L], I),
-    "pb_gemm_tc_scratch_bytes": ([I, I, I], L),
-    "pb_gemm_tc_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, P, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
     "pb_decode_advance": ([P, P, P, P, P, I, I, P], I),
 }

@@ -9,16 +9,13 @@ bfloat16, float32 accumulation:
     (bulk copies into a shared-memory ring that start before the previous kernel
     has finished, mma.sync, every block owning whole output features);
   * cuBLAS through torch.mm above 16 rows, which is where the reference's own
-    dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433);
-  * the tcgen05 kernel of this library (TMA, tensor memory, a persistent grid that
-    balances the stream of weight bytes over all blocks) when PRELUDE_TC_GEMM=all
-    asks for it: measured behind cuBLAS at every shape above 16 rows.
+    dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433).
 """
 from __future__ import annotations
 
 import contextlib
 import os
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -28,10 +25,6 @@ from .library import KernelLibraryError, check
 
 # rows up to which the streaming kernel is used (0 turns it off; it takes 16 at most)
 STREAM_MAX_ROWS = int(os.environ.get("PRELUDE_STREAM_MAX_ROWS", "16"))
-# "all" sends the products of more than 16 rows to the tcgen05 kernel instead of cuBLAS
-TC_POLICY = os.environ.get("PRELUDE_TC_GEMM", "auto")
-
-_retired: List[torch.Tensor] = []          # outgrown buffers that captured graphs may still use
 
 
 def stream_takes(x: torch.Tensor, weight: torch.Tensor, splits: int = 1) -> bool:
@@ -78,51 +71,6 @@ def gated_linear_silu(x: torch.Tensor, weight_gate_up: torch.Tensor) -> Optional
     return None
 
 
-# Whether a decode step's gated feed-forward runs as one launch (PRELUDE_MLP_CHAIN=1).  Off: measured on B200 at
-# Qwen3-4B sizes, the one launch takes 30.7 us against 28.9 us for the two launches it replaces (the barrier between
-# its two products and the fetch of the new input cost as much as the boundary between two kernels that were
-# launched ahead of time, and the ring is no deeper), and the batch-8 decode step 2.75 ms against 2.63 ms.
-MLP_CHAIN = os.environ.get("PRELUDE_MLP_CHAIN", "0") == "1"
-
-_chain_counters: Dict[torch.device, torch.Tensor] = {}
-
-
-def _chain_counters_for(device: torch.device) -> torch.Tensor:
-    """The counters of the chain kernel's barriers: zero before the first launch, and every launch leaves them
-    zero.  Launches on one stream follow one another, so they share them."""
-    c = _chain_counters.get(device)
-    if c is None:
-        c = _chain_counters[device] = torch.zeros(_l.library().pb_mlp_chain_counters(), dtype=torch.int32, device=device)
-    return c
-
-
-def gated_mlp_chain(x: torch.Tensor, weight_gate_up: torch.Tensor, weight_down: torch.Tensor):
-    """down(silu(gate(x)) * up(x)) for the few rows of a decode step in ONE launch (csrc/gemm_chain.cu): the weights
-    of the down projection follow those of gate/up through the same ring of shared-memory stages.  Returns the
-    result as ``PartialSums`` (K of the down projection cut as ``stream_splits`` says), or None where the kernel
-    does not take the shapes - the caller then launches the products one by one."""
-    if x.dtype != torch.bfloat16 or weight_gate_up.dtype != torch.bfloat16 or weight_down.dtype != torch.bfloat16:
-        return None
-    M, H = x.shape
-    I = weight_gate_up.shape[0] // 2
-    if (not 0 < M <= min(STREAM_MAX_ROWS, 16) or weight_gate_up.shape[0] != 2 * I or weight_gate_up.shape[1] != H
-            or tuple(weight_down.shape) != (H, I) or x.stride(1) != 1 or weight_gate_up.stride(1) != 1 or weight_down.stride(1) != 1
-            or x.data_ptr() % 16 or weight_gate_up.data_ptr() % 16 or weight_down.data_ptr() % 16):
-        return None
-    lib = _l.library()
-    splits = stream_splits(M, H, I)
-    if not lib.pb_mlp_chain_supported(M, H, I, splits, x.stride(0), weight_gate_up.stride(0), weight_down.stride(0)):
-        return None
-    act = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
-    parts = torch.empty((splits, M, H), dtype=torch.float32, device=x.device)
-    check(lib.pb_mlp_chain_bf16(x.data_ptr(), x.stride(0), weight_gate_up.data_ptr(), weight_gate_up.stride(0),
-                                weight_down.data_ptr(), weight_down.stride(0), act.data_ptr(), parts.data_ptr(), M, H, I, splits,
-                                _chain_counters_for(x.device).data_ptr(), tc_status(x.device).data_ptr(),
-                                _l.current_stream_ptr(x.device)), "mlp_chain")
-    return K.PartialSums(parts)
-
-
-_tc_scratch: Dict[torch.device, torch.Tensor] = {}
 _tc_status: Dict[torch.device, torch.Tensor] = {}
 _step_status: Optional[torch.Tensor] = None
 
@@ -149,47 +97,6 @@ def tc_status(device: torch.device) -> torch.Tensor:
     if st is None:
         st = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
     return st
-
-
-def _tc_scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
-    buf = _tc_scratch.get(device)
-    if buf is None or buf.numel() < nbytes:
-        if buf is not None:
-            _retired.append(buf)
-        buf = torch.zeros(max(nbytes, 48 << 20), dtype=torch.uint8, device=device)
-        _tc_scratch[device] = buf
-    return buf
-
-
-def tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    M, Kdim = x.shape
-    if x.stride(1) != 1 or weight.stride(1) != 1 or x.data_ptr() % 16 or weight.data_ptr() % 16:
-        return False
-    return bool(_l.library().pb_gemm_tc_supported(M, weight.shape[0], Kdim, x.stride(0), weight.stride(0)))
-
-
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """x W^T on tcgen05: x is the 128-row operand (rows that do not exist are zero-filled
-    by the copy engine), the weights stream through as the wide one."""
-    M, Kdim = x.shape
-    N = weight.shape[0]
-    if out_dtype not in (torch.bfloat16, torch.float32):
-        raise KernelLibraryError("gemm_tc: output must be bfloat16 or float32")
-    lib = _l.library()
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    scratch = _tc_scratch_for(x.device, lib.pb_gemm_tc_scratch_bytes(M, N, Kdim))
-    check(lib.pb_gemm_tc_bf16(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(),
-                              M, N, Kdim, x.stride(0), weight.stride(0), out.stride(0), 1,
-                              1 if out_dtype == torch.float32 else 0, scratch.data_ptr(), tc_status(x.device).data_ptr(),
-                              _l.current_stream_ptr(x.device)), "gemm_tc")
-    return out
-
-
-def _tc_wanted(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> bool:
-    """Measured on B200 against cuBLAS, the tcgen05 kernel of this library is behind at every shape
-    that reaches this point (more than 16 rows), so it runs only when asked for."""
-    return TC_POLICY == "all"
 
 
 def stream_splits(M: int, N: int, Kdim: int) -> int:
@@ -219,8 +126,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             return K.PartialSums(gemm_stream(x, weight, bias, out_dtype, splits=splits))
         if stream_takes(x, weight):
             return gemm_stream(x, weight, bias, out_dtype)
-        if _tc_wanted(x, weight, out_dtype) and tc_takes(x, weight):
-            return gemm_tc(x, weight, bias, out_dtype)
         if out_dtype == torch.bfloat16:
             y = torch.mm(x, weight.t())
         else:

@@ -14,7 +14,7 @@ import torch
 
 from ..config.spec import GatedMlpSpec
 from ..ops import kernels as K
-from ..ops.linear import MLP_CHAIN, gated_linear_silu, gated_mlp_chain, linear
+from ..ops.linear import gated_linear_silu, linear
 from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
 
@@ -53,10 +53,6 @@ class GatedMlp:
     def forward(self, x: torch.Tensor):
         """The feed-forward of x; what comes back goes to a fused residual add, which also takes
         the partial sums of a product whose K was cut into parts."""
-        if MLP_CHAIN and self.spec.activation == "silu":
-            y = gated_mlp_chain(x, self.w_gate_up, self.w_down)          # a step of few tokens: one launch for both products
-            if y is not None:
-                return y
         act = gated_linear_silu(x, self.w_gate_up) if self.spec.activation == "silu" else None
         if act is None:
             act = _ACTIVATIONS[self.spec.activation](linear(x, self.w_gate_up))

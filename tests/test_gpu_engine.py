@@ -103,45 +103,6 @@ def test_f32_cuts_agree_bitwise(folders, which):
             assert torch.equal(row, other[key]), f"{key}: cuts disagree by {(row - other[key]).abs().max():.3e}"
 
 
-@pytest.mark.parametrize("which", ["A", "B"])
-@pytest.mark.parametrize("cut", ["whole", "tail_decode", "mixed"])
-def test_bf16_with_every_product_on_the_tcgen05_kernel(folders, monkeypatch, which, cut):
-    """The same comparison with all linear layers (prompt portions and decode steps) on the
-    library's own tensor-core product instead of cuBLAS."""
-    from prelude_b200.ops import linear
-    monkeypatch.setattr(linear, "TC_POLICY", "all")
-    monkeypatch.setattr(linear, "STREAM_MAX_ROWS", 0)           # decode steps too
-    folder = folders[(which, torch.bfloat16)]
-    reqs = _requests(which)
-    ref = _reference(which, folder, reqs)
-    page = tiny.PARAMS[which][2]
-    schedule = {"whole": harness.whole, "tail_decode": harness.tail_decode, "mixed": harness.mixed}[cut](reqs)
-    runner = _runner(folder, torch.bfloat16, page, harness.peak_tokens(schedule, page) // page)
-    _compare(harness.run_schedule(runner, schedule), ref, torch.bfloat16)
-    assert int(linear.tc_status(torch.device("cuda:0")).item()) == 0
-
-
-@pytest.mark.parametrize("which", ["A", "B"])
-@pytest.mark.parametrize("cut", ["tail_decode", "mixed"])
-def test_bf16_with_the_feed_forward_of_small_steps_in_one_launch(folders, monkeypatch, which, cut):
-    """The same comparison with the feed-forward of every step of up to 16 tokens on the chain kernel (off by
-    default): single decoded tokens, short portions, and the steps that mix them."""
-    from prelude_b200.ops import linear
-    from prelude_b200.parts import mlp
-    monkeypatch.setattr(mlp, "MLP_CHAIN", True)
-    calls = []
-    chain = mlp.gated_mlp_chain
-    monkeypatch.setattr(mlp, "gated_mlp_chain", lambda *a: calls.append(1) or chain(*a))
-    folder = folders[(which, torch.bfloat16)]
-    reqs = _requests(which)
-    ref = _reference(which, folder, reqs)
-    page = tiny.PARAMS[which][2]
-    schedule = {"tail_decode": harness.tail_decode, "mixed": harness.mixed}[cut](reqs)
-    runner = _runner(folder, torch.bfloat16, page, harness.peak_tokens(schedule, page) // page)
-    _compare(harness.run_schedule(runner, schedule), ref, torch.bfloat16)
-    assert len(calls) > 0 and int(linear.tc_status(torch.device("cuda:0")).item()) == 0
-
-
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("which", ["A", "C", "E"])
 def test_the_first_tokens_of_a_sequence(folders, which, dtype):

@@ -613,58 +613,6 @@ def test_gemm_stream_gated(M, I, K_):
     assert gated_linear_silu(rnd(40, K_, dtype=torch.bfloat16), w) is None      # too many rows: the caller takes two steps
 
 
-@pytest.mark.parametrize("M,H,I", [(8, 2560, 9728), (1, 64, 128), (16, 96, 160), (5, 1504, 8192), (3, 4096, 12288), (9, 2560, 9728)])
-def test_gated_feed_forward_in_one_launch(M, H, I):
-    # down(silu(gate(x)) * up(x)) from the chain kernel: against float64 (with the activation rounded to bfloat16 as
-    # the kernel stores it), against the two launches it replaces, and twice in a row (the barrier's counters)
-    from prelude_b200.ops.kernels import PartialSums
-    from prelude_b200.ops.linear import gated_mlp_chain, gemm_stream, linear, tc_status
-    x = rnd(M, H, dtype=torch.bfloat16, seed=71)
-    w1, w2 = rnd(2 * I, H, dtype=torch.bfloat16, seed=72, scale=0.05), rnd(H, I, dtype=torch.bfloat16, seed=73, scale=0.05)
-    g, u = x.double() @ w1[:I].double().T, x.double() @ w1[I:].double().T
-    act = (g / (1 + torch.exp(-g)) * u).to(torch.bfloat16).double()
-    want = act @ w2.double().T
-    scale = float(want.abs().max())
-    for call in range(2):
-        got = gated_mlp_chain(x, w1, w2)
-        assert isinstance(got, PartialSums) and got.shape == (M, H)
-        total = got.parts.double().sum(0)
-        assert (total - want).abs().max() <= 4e-3 * scale, call
-    two = linear(gemm_stream(x, w1, gated=True), w2, partial_sums_ok=True)
-    two = two.parts.sum(0) if isinstance(two, PartialSums) else two.float()
-    assert (total.float() - two).abs().max() <= tol(torch.bfloat16, scale)
-    wide = rnd(M, H + 64, dtype=torch.bfloat16, seed=74)               # x as a view into a wider tensor
-    a = gated_mlp_chain(wide[:, 32:32 + H], w1, w2).parts
-    b = gated_mlp_chain(wide[:, 32:32 + H].contiguous(), w1, w2).parts
-    assert torch.equal(a, b)
-    assert int(tc_status(x.device).item()) == 0
-
-
-def test_gated_feed_forward_in_one_launch_finds_the_one_path_that_matters():
-    # one large weight at the far end of each matrix, everything else small: a lost stage, chunk or part of K shows
-    from prelude_b200.ops.linear import gated_mlp_chain
-    M, H, I = 5, 2560, 9728
-    x = rnd(M, H, dtype=torch.bfloat16, seed=1, scale=0.01)
-    w1, w2 = rnd(2 * I, H, dtype=torch.bfloat16, seed=2, scale=0.01), rnd(H, I, dtype=torch.bfloat16, seed=3, scale=0.01)
-    for (m, k, i, n) in [(0, 0, 0, 0), (4, H - 1, I - 1, H - 1), (2, 1297, 2431, 17), (3, 2048, 2432, 1300), (1, 31, 7295, 2559)]:
-        x2, w1b, w2b = x.clone(), w1.clone(), w2.clone()
-        x2[m, k] = 4.0
-        w1b[i, k], w1b[I + i, k] = 2.0, 2.0                            # gate = up = 8 at feature i: silu(8) * 8 = 63.98
-        w2b[:, i] = 0.0                                                # the large activation reaches one output only
-        w2b[n, i] = 1.0
-        got = gated_mlp_chain(x2, w1b, w2b).parts.sum(0)
-        assert abs(float(got[m, n]) - 63.98) < 1.0, (m, k, i, n)
-        got[m, n] = 0
-        assert float(got.abs().max()) < 1.0
-
-
-def test_gated_feed_forward_in_one_launch_leaves_other_shapes_to_the_caller():
-    from prelude_b200.ops.linear import gated_mlp_chain
-    assert gated_mlp_chain(rnd(40, 64, dtype=torch.bfloat16), rnd(256, 64, dtype=torch.bfloat16), rnd(64, 128, dtype=torch.bfloat16)) is None
-    assert gated_mlp_chain(rnd(4, 96, dtype=torch.bfloat16), rnd(400, 96, dtype=torch.bfloat16), rnd(96, 200, dtype=torch.bfloat16)) is None   # 200 % 16
-    assert gated_mlp_chain(rnd(4, 64), rnd(256, 64), rnd(64, 128)) is None                                                            # float32
-
-
 def test_gemm_stream_finds_the_one_weight_that_matters():
     # one large product at the far end of K and of N, everything else small: a lost chunk or row shows
     from prelude_b200.ops.linear import gemm_stream
@@ -692,33 +640,3 @@ def test_gemm_stream_refuses_other_shapes_and_linear_falls_back():
     assert stream_takes(rnd(8, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16))
 
 
-# ---------------------------------------------------------------------------------------
-# the tcgen05 product (TMA, tensor memory)
-# ---------------------------------------------------------------------------------------
-@pytest.mark.parametrize("M,N,K_", [(8, 128, 64), (1, 2560, 4096), (8, 6144, 2560), (5, 200, 72), (33, 2560, 9728),
-                                    (64, 1000, 1024), (16, 331, 200), (65, 256, 64), (128, 256, 256), (300, 2560, 4096),
-                                    (2048, 6144, 2560), (130, 331, 200), (1000, 19456, 2560)])
-def test_gemm_tc_against_float32(M, N, K_):
-    from prelude_b200.ops.linear import gemm_tc, tc_status
-    x, w, b = rnd(M, K_, dtype=torch.bfloat16, seed=31), rnd(N, K_, dtype=torch.bfloat16, seed=32, scale=0.05), rnd(N, seed=33)
-    want = x.float() @ w.float().T
-    scale = float(want.abs().max())
-    got = gemm_tc(x, w)
-    assert got.dtype == torch.bfloat16 and (got.float() - want).abs().max() <= tol(torch.bfloat16, scale)
-    got32 = gemm_tc(x, w, b, torch.float32)
-    assert got32.dtype == torch.float32 and (got32 - (want + b)).abs().max() <= 2e-5 * scale * 4
-    assert torch.equal(gemm_tc(x, w), got)                           # counters back at zero, the same sums again
-    wide = rnd(M, K_ + 64, dtype=torch.bfloat16, seed=34)            # x as a view into a wider tensor
-    assert torch.equal(gemm_tc(wide[:, 32:32 + K_], w), gemm_tc(wide[:, 32:32 + K_].contiguous(), w))
-    assert int(tc_status(x.device).item()) == 0
-
-
-def test_gemm_tc_refuses_unaligned_rows():
-    from prelude_b200.ops.library import KernelLibraryError
-    from prelude_b200.ops.linear import gemm_tc, linear, tc_takes
-    x, w = rnd(4, 68, dtype=torch.bfloat16), rnd(40, 68, dtype=torch.bfloat16)      # rows of 136 bytes
-    assert not tc_takes(x, w)
-    with pytest.raises(KernelLibraryError, match="not taken"):
-        gemm_tc(x, w)
-    want = x.double() @ w.double().T
-    assert (linear(x, w, None, torch.float32).double() - want).abs().max() <= 1e-3 * float(want.abs().max())
