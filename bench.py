@@ -194,12 +194,42 @@ def time_decode(engine, cfg, batch, steps, warmup, seed):
     status = int(graph.status.item())
     if status != 0:
         raise RuntimeError(f"decode loop raised kernel status {status}")
+    if TIMELINE:
+        print_timeline(graph)
     for rid in rids:
         runner.finish(rid)
     del graph
     avg_ctx = PREFIX_LEN + warmup + (steps + 1) / 2.0
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches_per_step": None,
             "avg_ctx": avg_ctx, "window": (t0, t1)}, library
+
+
+TIMELINE = False
+
+
+def print_timeline(graph):
+    """One more replay of the captured step with the kernels' timeline marks on (a library built with
+    PRELUDE_TIMELINE=1): for every kernel of the step's second layer, when its first block started, when the kernel
+    before it had finished, when its input had arrived and when its first and last block were done, in
+    microseconds from the layer's first mark."""
+    import torch
+    from prelude_b200.ops import timeline
+    timeline.enable()
+    timeline.reset()
+    graph.replay()
+    torch.cuda.synchronize()
+    marks = timeline.read()
+    # a layer begins with the add+norm that precedes the qkv product: cut the step at every second norm entry
+    starts = [i for i, m in enumerate(marks) if m.kernel == "add_rmsnorm" and m.mark == "entry" and not m.last_block]
+    if len(starts) < 5:
+        print(f"timeline: {len(marks)} marks, too few to show a layer", file=sys.stderr)
+        return
+    lo, hi = starts[2], starts[4]                           # the second layer's two norms and what lies between
+    t0 = marks[lo].ns
+    print("timeline of one layer of the captured decode step (us from the layer's first mark):", file=sys.stderr)
+    for m in marks[lo:hi]:
+        print(f"  {(m.ns - t0) / 1e3:8.2f}  {m.kernel:22s} {m.mark:10s} {'last block' if m.last_block else 'first block'}", file=sys.stderr)
+    print(f"  {(marks[hi].ns - t0) / 1e3:8.2f}  next layer begins", file=sys.stderr)
 
 
 def time_prefill(engine, cfg, warmup, reps=3):
@@ -300,7 +330,7 @@ def serve(args):
 
 
 def main():
-    global MODEL, PREFIX_LEN, CONTEXT_LEN, PAGE_SIZE, PREFILL_TOKENS
+    global MODEL, PREFIX_LEN, CONTEXT_LEN, PAGE_SIZE, PREFILL_TOKENS, TIMELINE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -314,6 +344,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt (the contract's is 2,048)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the kernels' timeline of one layer of the decode step to stderr (needs PRELUDE_TIMELINE=1 in the environment)")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
                     help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own)")
     ap.add_argument("--requests", type=int, default=32, help="serving: number of requests")
@@ -329,6 +361,7 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus N with N > 1 is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    TIMELINE = args.timeline
     if args.model_size != "4b":
         MODEL = dict(QWEN3_4B, **OTHER_SIZES[args.model_size])
     PREFIX_LEN = args.prefix_len

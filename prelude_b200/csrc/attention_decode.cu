@@ -59,6 +59,8 @@
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
 
+PB_TIMELINE_UNIT(attention_decode)
+
 #define DEC_LOADERS 128         // threads of the lsu path's four loader warps
 #define DEC_MAX_CLUSTER 16      // blocks of one (token, key/value head) that may form a thread-block cluster
 #define DEC_MAX_PAGES 512       // page ids of one block's share kept in shared memory (else read from the table)
@@ -99,6 +101,7 @@ __device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
 template <int DMAX, bool BULK, bool PAIR>
 __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PAIR ? 2 : 1)) attn_decode_kernel(DecodeParams dp) {
     pb_grid_dep_launch();
+    PB_TL(PB_TL_ATTN_DECODE, PB_TL_ENTRY);
     using T = DecodeTiling<DMAX, BULK, PAIR>;
     constexpr int DEC_THREADS = T::THREADS;
     const AttnParams& p = dp.a;
@@ -152,6 +155,7 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
         const bool holds_newest = kt1 == kt_hi;             // this block's last tile is the request's last
         if (warp < 4) {
             pb_grid_dep_wait();
+            PB_TL(PB_TL_ATTN_DECODE, PB_TL_AFTER_WAIT);
             // q rows of the group (rows from G on are zero)
             for (int c = threadIdx.x; c < 16 * chunks; c += 128) {
                 const int row = c / chunks, ch = c - row * chunks;
@@ -162,6 +166,7 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
             cp_async_commit();
             cp_async_wait<0>();
             asm volatile("bar.sync 1, 128;\n" ::: "memory");   // q is ready (the four consumer warps only)
+            PB_TL(PB_TL_ATTN_DECODE, PB_TL_INPUT);
         }
 
         const int n_tiles = (kt1 - kt0 + 1) * (BN / BNW);   // consumer tiles of BNW keys; tile i belongs to warp i % NC
@@ -341,6 +346,7 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
             }
         }
     }
+    PB_TL(PB_TL_ATTN_DECODE, PB_TL_DONE);
     if (p.n_splits == 1) return;
     if (dp.cluster) {
         // The cluster is the (token, key/value head)'s splits, in order: block rank = split.  After the barrier every
@@ -377,6 +383,7 @@ __global__ void __launch_bounds__((DecodeTiling<DMAX, BULK, PAIR>::THREADS), (PA
             p.out[th0 * d + idx] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
         }
         cluster.sync();
+        PB_TL(PB_TL_ATTN_DECODE, PB_TL_EXIT);
         return;
     }
     // count this split in; the last one adds all splits up, in ascending order

@@ -29,6 +29,11 @@ LIB_NAME = "libprelude_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
+# PRELUDE_TIMELINE=1 compiles the kernels' timeline marks in (see common.cuh): another set of objects, another library
+if os.environ.get("PRELUDE_TIMELINE", "0") == "1":
+    NVCC_FLAGS = NVCC_FLAGS + ["-DPB_TIMELINE"]
+    LIB_NAME = "libprelude_b200_timeline.so"
+OBJ_PREFIX = "tl__" if LIB_NAME != "libprelude_b200.so" else ""
 
 
 def _say(msg: str) -> None:
@@ -111,7 +116,7 @@ def existing_library() -> Optional[str]:
               os.path.join(tempfile.gettempdir(), f"prelude_b200_build_{os.getuid()}")):
         if not d:
             continue
-        stamp, lib = os.path.join(d, "build.json"), os.path.join(d, LIB_NAME)
+        stamp, lib = os.path.join(d, LIB_NAME + ".json"), os.path.join(d, LIB_NAME)
         try:
             with open(stamp) as f:
                 if json.load(f).get("hash") == want and os.path.isfile(lib):
@@ -136,7 +141,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for name in sources():
         src = os.path.join(SRC_DIR, name)
         key = _sha([src] + hdr_paths, flags_key)
-        obj = os.path.join(out, f"{name[:-3]}.{key}.o")
+        obj = os.path.join(out, f"{OBJ_PREFIX}{name[:-3]}.{key}.o")
         objs.append(obj)
         if force or not os.path.isfile(obj):
             jobs.append((name, src, obj))
@@ -159,12 +164,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if proc.returncode != 0:
         raise RuntimeError(f"linking {LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")
     os.replace(tmp, lib)
-    with open(os.path.join(out, "build.json"), "w") as f:
+    with open(os.path.join(out, LIB_NAME + ".json"), "w") as f:
         json.dump({"hash": source_hash(), "sources": sources(), "built": time.time()}, f)
     # drop objects of older source versions
     keep = {os.path.basename(o) for o in objs}
     for f in os.listdir(out):
-        if f.endswith(".o") and f not in keep:
+        if f.endswith(".o") and f not in keep and f.startswith("tl__") == bool(OBJ_PREFIX):
             try:
                 os.remove(os.path.join(out, f))
             except OSError:

@@ -100,6 +100,43 @@ __host__ __device__ __forceinline__ int pb_kv_elem_offset(int elem, int token_in
     return swizzle ? ((((elem >> 3) ^ (token_in_page & 7)) << 3) | (elem & 7)) : elem;
 }
 
+// ---------------------------------------------------------------------------
+// A timeline of a step's kernels, for looking at what happens between them
+// (compiled in with -DPB_TIMELINE, which PRELUDE_TIMELINE=1 asks the build
+// for; without it the marks are nothing).  A source file that has marks says
+// PB_TIMELINE_UNIT(name) once: that gives it the pointer to the record and
+// the exported setter pb_timeline_set_<name>.  PB_TL(kernel, mark) then stores
+// the device-wide nanosecond clock, by thread 0 of the grid's first and of
+// its last block: word 0 of the record counts the entries, entry = kernel (8
+// bits) | mark (4) | last block (1) | time (51 bits).
+// ---------------------------------------------------------------------------
+#ifdef PB_TIMELINE
+#define PB_TL_CAP 8192
+__device__ __forceinline__ void pb_tl_mark(unsigned long long* tl, int kernel, int mark) {
+    if (tl == nullptr || threadIdx.x != 0) return;
+    const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    const bool last = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1;
+    if (!first && !last) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    const unsigned i = atomicAdd(reinterpret_cast<unsigned*>(tl), 1u);
+    if (i < PB_TL_CAP)
+        tl[1 + i] = ((unsigned long long)(kernel & 0xff) << 56) | ((unsigned long long)(mark & 0xf) << 52) |
+                    ((unsigned long long)(first ? 0 : 1) << 51) | (t & 0x7FFFFFFFFFFFFull);
+}
+#define PB_TIMELINE_UNIT(name)                                                                   \
+    static __device__ unsigned long long* g_pb_tl = nullptr;                                     \
+    PB_API int pb_timeline_set_##name(unsigned long long* record) {                              \
+        return cudaMemcpyToSymbol(g_pb_tl, &record, sizeof(record)) == cudaSuccess ? 0 : 1;      \
+    }
+#define PB_TL(kernel, mark) pb_tl_mark(g_pb_tl, kernel, mark)
+#else
+#define PB_TIMELINE_UNIT(name)
+#define PB_TL(kernel, mark) do { } while (0)
+#endif
+enum PbTimelineKernel : int { PB_TL_NORM = 1, PB_TL_GEMM_STREAM = 2, PB_TL_ROPE = 3, PB_TL_ATTN_DECODE = 4 };
+enum PbTimelineMark : int { PB_TL_ENTRY = 0, PB_TL_AFTER_WAIT = 1, PB_TL_INPUT = 2, PB_TL_DONE = 3, PB_TL_EXIT = 4 };
+
 // Dispatch a launcher body on an element type code.
 #define PB_DISPATCH_DTYPE(code, T, ...)                              \
     do {                                                             \

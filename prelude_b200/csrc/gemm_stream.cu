@@ -45,6 +45,8 @@
 // memory beside the ring (pb_gemm_stream_supported says whether a shape is taken).
 #include "attention_common.cuh"
 
+PB_TIMELINE_UNIT(gemm_stream)
+
 #define GS_WARPS 8                              // compute warps
 #define GS_LOADERS 4                            // loader warps; each issues GS_ROWS / GS_LOADERS copies per stage
 #define GS_THREADS ((GS_WARPS + GS_LOADERS) * 32)
@@ -86,6 +88,7 @@ __device__ __forceinline__ void ldmatrix_x2(unsigned& r0, unsigned& r1, unsigned
 template <int MT>
 __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) {
     pb_grid_dep_launch();
+    PB_TL(PB_TL_GEMM_STREAM, PB_TL_ENTRY);
     if (gridDim.y > 1) {
         // K is cut into gridDim.y equal parts (p.K is the length of one); part s multiplies its columns of W with
         // its columns of x and writes a partial output of its own, which the reader adds up
@@ -159,6 +162,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
 
     // ---------------- compute warps ----------------
     pb_grid_dep_wait();                                        // the output may still be in use by the kernel before
+    PB_TL(PB_TL_GEMM_STREAM, PB_TL_AFTER_WAIT);
     const int g = lane >> 2, t4 = lane & 3;
     if (warp < GS_LOADERS) {
         // x is this kernel's only input that another kernel writes: the first four compute warps fetch it the
@@ -175,6 +179,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
     }
     gs_bar_compute();
     if (*(volatile int*)&s_dead) return;
+    PB_TL(PB_TL_GEMM_STREAM, PB_TL_INPUT);
     const unsigned sX_a = smem_u32(sX), ring_a = smem_u32(ring);
     // ldmatrix lanes.  W (row operand, 16 features x 16 k): lane -> feature lane & 15 (the first eight in one
     // stage, the others in the next), k half lane >> 4.  x (column operand): 8 batch rows x 16 k (x2), or
@@ -288,6 +293,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
         }
         gs_bar_compute();                                      // the sums are read before the next tile overwrites them
     }
+    PB_TL(PB_TL_GEMM_STREAM, PB_TL_DONE);
 }
 
 // ---------------------------------------------------------------------------------------

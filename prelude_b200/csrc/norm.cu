@@ -14,6 +14,9 @@
 // whatever else is in the batch.
 #include "common.cuh"
 
+
+PB_TIMELINE_UNIT(norm)
+
 __device__ __forceinline__ float block_sum(float v, float* smem) {
     v = pb_warp_sum(v);
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -60,6 +63,7 @@ template <typename TX, typename TY, int ITERS>
 __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride, float* __restrict__ res,
                                         const float* __restrict__ w, TY* __restrict__ y, int width, float eps) {
     pb_grid_dep_launch();
+    PB_TL(PB_TL_NORM, PB_TL_ENTRY);
     __shared__ float red[32];
     size_t row = blockIdx.x;
     float4* r4 = reinterpret_cast<float4*>(res + row * width);
@@ -73,6 +77,7 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
         if (i < n4) scale[it] = w4[i];
     }
     pb_grid_dep_wait();
+    PB_TL(PB_TL_NORM, PB_TL_AFTER_WAIT);
     float4 keep[ITERS];
     float ss = 0.f;
 #pragma unroll
@@ -126,6 +131,7 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
             }
         }
     }
+    PB_TL(PB_TL_NORM, PB_TL_DONE);
 }
 
 static int norm_threads(int width) {

@@ -106,6 +106,8 @@ __global__ void qknorm_rope_kvwrite_kernel(
     }
 }
 
+PB_TIMELINE_UNIT(rope)
+
 // The vector kernel: LANES = head_dim / 8 lanes per (token, head), 8 elements each.
 template <int LANES>
 __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
     int n_tokens, int n_heads, int n_kv_heads, int write_kv, int swizzle, int* __restrict__ status) {
     pb_grid_dep_launch();
+    PB_TL(PB_TL_ROPE, PB_TL_ENTRY);
     constexpr int D = LANES * 8;
     const int heads_per_token = n_heads + (write_kv ? 2 * n_kv_heads : 0);
     const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;     // (token, head) of this lane
@@ -174,6 +177,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
         }
     }
     pb_grid_dep_wait();
+    PB_TL(PB_TL_ROPE, PB_TL_AFTER_WAIT);
     const uint4 raw = *reinterpret_cast<const uint4*>(src);
     if (!is_q && !is_k) {                                                                    // values: plain copy
         if (store) *reinterpret_cast<uint4*>(dst) = raw;
@@ -213,6 +217,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
         for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
         *reinterpret_cast<uint4*>(dst) = out;
     }
+    PB_TL(PB_TL_ROPE, PB_TL_DONE);
 }
 
 template <int LANES, typename... Args>

@@ -38,7 +38,8 @@ def test_embed_gather(dtype, T, H, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("T,H", [(1, 64), (19, 2560), (3, 100), (2, 8192), (4, 9000), (7, 72)])
+@pytest.mark.parametrize("T,H", [(1, 64), (19, 2560), (3, 100), (2, 8192), (4, 9000), (7, 72), (32, 5120), (1, 1024),
+                                 (33, 4096), (8, 1100)])
 @pytest.mark.parametrize("eps", [1e-6, 1e-3])
 def test_add_rmsnorm(dtype, T, H, eps):
     x, res, w = rnd(T, H, dtype=dtype, seed=1), rnd(T, H, seed=2), 1 + 0.3 * rnd(H, seed=3)
@@ -65,7 +66,8 @@ def test_add_rmsnorm(dtype, T, H, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("T,H,parts", [(8, 2560, 4), (3, 100, 2), (1, 64, 1), (5, 9000, 3), (7, 74, 5)])
+@pytest.mark.parametrize("T,H,parts", [(8, 2560, 4), (3, 100, 2), (1, 64, 1), (5, 9000, 3), (7, 74, 5), (16, 4096, 2),
+                                       (1, 5120, 6)])
 def test_add_rmsnorm_of_partial_sums(dtype, T, H, parts):
     # the addend as float32 parts to be added up (a product whose K was cut): same result as adding their sum
     from prelude_b200.ops.kernels import PartialSums
