@@ -10,9 +10,10 @@
 //  crates/prelude-cuda/src/kernels/kernels_src/kvcache/knorm_rope_kv_write.cu:17-113,
 //  crates/prelude-cuda/src/kernels/kernels_src/kvcache/scatter_kv_cache.cu:32-46);
 // here q, k and v are handled by one launch.  The rotation pairs element j with
-// j + rotary_dim/2 (crates/prelude-core/src/models/commons/attn_utils.rs:52-59);
-// elements from rotary_dim on pass through.  cos/sin are float32 tables
-// [max_positions, rotary_dim/2].
+// j + rotary_dim/2 (crates/prelude-core/src/models/commons/attn_utils.rs:52-59),
+// or, with `interleaved`, element 2j with 2j + 1 (what architectures with
+// adjacent pairs need; the position part says which); elements from rotary_dim
+// on pass through.  cos/sin are float32 tables [max_positions, rotary_dim/2].
 //
 // One warp per (token, head) in the general kernel.  bfloat16 rows whose head
 // size is a power of two up to 256 take the vector kernel: 16 bytes per lane,
@@ -29,7 +30,7 @@ __global__ void qknorm_rope_kvwrite_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long token_stride,
     T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
     const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int max_positions,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int interleaved, int max_positions,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
     int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv, int swizzle, int* __restrict__ status) {
@@ -93,11 +94,12 @@ __global__ void qknorm_rope_kvwrite_kernel(
         return;
     }
     for (int j = lane; j < half; j += 32) {
-        float a = pb_ld(src + j) * inv, b = pb_ld(src + j + half) * inv;
-        if (weight != nullptr) { a *= weight[j]; b *= weight[j + half]; }
+        const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;      // the pair that angle j turns
+        float a = pb_ld(src + ia) * inv, b = pb_ld(src + ib) * inv;
+        if (weight != nullptr) { a *= weight[ia]; b *= weight[ib]; }
         float c = cos_table[(size_t)pos * half + j], s = sin_table[(size_t)pos * half + j];
-        pb_st(dst + pb_kv_elem_offset(j, in_page, swz), a * c - b * s);
-        pb_st(dst + pb_kv_elem_offset(j + half, in_page, swz), b * c + a * s);
+        pb_st(dst + pb_kv_elem_offset(ia, in_page, swz), a * c - b * s);
+        pb_st(dst + pb_kv_elem_offset(ib, in_page, swz), b * c + a * s);
     }
     for (int i = 2 * half + lane; i < head_dim; i += 32) {
         float a = pb_ld(src + i) * inv;
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     long long token_stride, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
     __nv_bfloat16* __restrict__ v_pages, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int max_positions,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim, int interleaved, int max_positions,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
     int n_tokens, int n_heads, int n_kv_heads, int write_kv, int swizzle, int* __restrict__ status) {
@@ -161,13 +163,17 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
     // rotation: element j of the first half pairs with j + half; the partner chunk sits half / 8 lanes away
     const int half = (cos_table != nullptr) ? rotary_dim / 2 : 0;
     const int hc = half / 8;                                                                 // chunks per half (0: no rotation)
-    const bool first = c < hc, second = c >= hc && c < 2 * hc;
+    // interleaved pairs (2j, 2j + 1) lie inside one lane's chunk: the chunk of elements 8c.. takes angles 4c..4c+3
+    const bool first = interleaved ? (c * 8 < 2 * half) : (c < hc), second = !interleaved && c >= hc && c < 2 * hc;
     const bool rotates = (first || second) && (is_q || is_k);
     float4 c0 = make_float4(1.f, 1.f, 1.f, 1.f), c1 = c0, s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
     if (rotates && !padding) {
         if (pos < 0 || pos >= max_positions) {
             if (live && c == 0 && status) atomicExch(status, 3);
             store = false;
+        } else if (interleaved) {
+            c0 = *reinterpret_cast<const float4*>(cos_table + (size_t)pos * half + c * 4);   // four angles for four pairs
+            s0 = *reinterpret_cast<const float4*>(sin_table + (size_t)pos * half + c * 4);
         } else {
             const int j0 = (first ? c : c - hc) * 8;
             const float* cp = cos_table + (size_t)pos * half + j0;
@@ -199,12 +205,20 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvwrite_vec_kernel(
         x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
         x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
     }
-    const int partner = first ? c + hc : (second ? c - hc : c);
+    const int partner = interleaved ? c : (first ? c + hc : (second ? c - hc : c));
     const int src_lane = (threadIdx.x & 31) - c + partner;
     float y[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[i] = __shfl_sync(0xffffffffu, x[i], src_lane);
-    if (rotates) {
+    if (rotates && interleaved) {
+        const float cs[4] = {c0.x, c0.y, c0.z, c0.w}, sn[4] = {s0.x, s0.y, s0.z, s0.w};
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const float a = x[2 * m], b = x[2 * m + 1];
+            x[2 * m] = a * cs[m] - b * sn[m];
+            x[2 * m + 1] = b * cs[m] + a * sn[m];
+        }
+    } else if (rotates) {
         const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
@@ -230,7 +244,7 @@ static void launch_rope_vec(long long rows, cudaStream_t stream, Args... args) {
 PB_API int pb_qknorm_rope_kvwrite(
     const void* q, const void* k, const void* v, long long token_stride, void* q_out, void* k_pages, void* v_pages,
     int dtype, const float* q_weight, const float* k_weight, float eps, const float* cos_table,
-    const float* sin_table, int rotary_dim, int max_positions, const int32_t* positions, const int32_t* token_seq,
+    const float* sin_table, int rotary_dim, int interleaved, int max_positions, const int32_t* positions, const int32_t* token_seq,
     const int32_t* block_table, int table_stride, int page_size, int num_pages, int n_tokens, int n_heads,
     int n_kv_heads, int head_dim, int write_kv, int swizzle, int* status, cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0, "qknorm_rope_kvwrite: bad sizes");
@@ -256,7 +270,7 @@ PB_API int pb_qknorm_rope_kvwrite(
         typedef __nv_bfloat16* B;
 #define PB_ROPE_VEC(L)                                                                                                  \
         launch_rope_vec<L>(warps, stream, (CB)q, (CB)k, (CB)v, token_stride, (B)q_out, (B)k_pages, (B)v_pages, q_weight,   \
-                           k_weight, eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq,           \
+                           k_weight, eps, cos_table, sin_table, rotary_dim, interleaved, max_positions, positions, token_seq, \
                            block_table, table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, write_kv,        \
                            swizzle, status)
         if (head_dim == 16) PB_ROPE_VEC(2);
@@ -274,7 +288,7 @@ PB_API int pb_qknorm_rope_kvwrite(
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(qknorm_rope_kvwrite_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream, 
             (const T*)q, (const T*)k, (const T*)v, token_stride, (T*)q_out, (T*)k_pages, (T*)v_pages, q_weight,
-            k_weight, eps, cos_table, sin_table, rotary_dim, max_positions, positions, token_seq, block_table,
+            k_weight, eps, cos_table, sin_table, rotary_dim, interleaved, max_positions, positions, token_seq, block_table,
             table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, head_dim, write_kv, swizzle, status)));
     PB_CHECK_LAUNCH("qknorm_rope_kvwrite");
     return 0;

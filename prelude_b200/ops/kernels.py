@@ -146,8 +146,10 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
                         positions: torch.Tensor, token_seq: Optional[torch.Tensor],
                         block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
                         v_pages: Optional[torch.Tensor], write_kv: bool,
-                        status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                        interleaved: bool = False) -> torch.Tensor:
     """q/k norm + rotation, q to a dense [T, nH, D] tensor (``out`` if given), k and v into their pages.
+    Angle j turns the pair (j, j + rotary_dim / 2), or with ``interleaved`` the pair (2 j, 2 j + 1).
 
     ``qkv`` is the merged projection [T, (nH + 2 nKV) D] (or [T, nH D] when
     nothing is written).  Pages are [num_pages, nKV, page_size, D].
@@ -196,7 +198,7 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_d
         base, base + q_cols * esz, base + (q_cols + kv_cols) * esz, qkv.stride(0), q_out.data_ptr(),
         _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, dtype_code(qkv.dtype),
         _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
-        max_pos, positions.data_ptr(), _ptr(token_seq), _ptr(block_table), stride, page_size, num_pages, T, n_heads,
+        1 if interleaved else 0, max_pos, positions.data_ptr(), _ptr(token_seq), _ptr(block_table), stride, page_size, num_pages, T, n_heads,
         n_kv_heads, head_dim, 1 if write_kv else 0, 1 if (write_kv and kv_swizzled(qkv.dtype, head_dim)) else 0,
         _ptr(status), _stream()), "qknorm_rope_kvwrite")
     return q_out

@@ -99,7 +99,8 @@ class Attention:
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm,
             s.qk_norm_eps if s.qk_norm_eps is not None else 0.0, self.position.cos, self.position.sin,
             self.position.rotary_dim, batch.positions, batch.table_row_of_token, table, cache.k_pages, cache.v_pages,
-            write_cache, batch.status, out=batch.workspace("attention_q", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype))
+            write_cache, batch.status, out=batch.workspace("attention_q", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype),
+            interleaved=bool(getattr(self.position, "interleaved", False)))
         o = paged_attention(q, cache.k_pages, cache.v_pages, batch, cache.group, s.softmax_scale, s.window,
                             out=batch.workspace("attention_out", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype))
         return linear(o.view(batch.n_tokens, self.q_cols), self.w_o, self.b_o)

@@ -11,8 +11,10 @@ Families and the calls the model makes on their members:
 
   norm          ``forward(x) -> y`` and ``add_forward(x, res) -> y`` (res += x in
                 place, float32; y = norm(res) in the run's type; x may be None).
-  position      ``tables() -> (cos, sin)`` or whatever its mixers understand; the
-                mixer owns the use of it.
+  position      what its mixers understand; the mixer owns the use of it.  The attention
+                mixer reads ``cos`` and ``sin`` (float32 [positions, rotary_dim / 2], or
+                None: no rotation), ``rotary_dim``, and ``interleaved`` (absent or False:
+                angle j turns elements j and j + rotary_dim / 2; True: 2 j and 2 j + 1).
   mixer         ``cache_need() -> KvPagesNeed | StateNeed | None`` and
                 ``forward(x, batch, cache, write_cache) -> y`` with x, y [T, hidden].
   feed_forward  ``forward(x) -> y``.

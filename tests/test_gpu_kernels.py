@@ -263,8 +263,9 @@ def test_attention_finds_the_one_key_that_matters(dtype, where):
 @pytest.mark.parametrize("nH,nKV,D,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 1, 48, 48), (8, 2, 128, 128),
                                           (3, 3, 80, 32), (2, 1, 256, 256), (2, 2, 64, 0), (4, 2, 128, 64),
                                           (4, 4, 64, 32), (2, 1, 128, 24), (32, 8, 128, 128), (3, 1, 32, 16)])
-@pytest.mark.parametrize("norm", [True, False])
-def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
+@pytest.mark.parametrize("norm,interleaved", [(True, False), (False, False), (True, True)])
+def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm, interleaved):
+    # interleaved: angle j turns elements 2 j and 2 j + 1 instead of j and j + rot / 2
     T, page, num_pages, eps, theta = 11, 8, 9, 1e-5, 10000.0
     qkv = rnd(T, (nH + 2 * nKV) * D, dtype=dtype, seed=1)
     qw, kw = (1 + 0.2 * rnd(D, seed=2), 1 + 0.2 * rnd(D, seed=3)) if norm else (None, None)
@@ -280,7 +281,8 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
     kp = torch.zeros(num_pages, nKV, page, D, dtype=dtype, device=DEV)
     vp = torch.zeros_like(kp)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    q_out = K().qknorm_rope_kvwrite(qkv, nH, nKV, D, qw, kw, eps, cos, sin, rot, positions, seq, table, kp, vp, True, status)
+    q_out = K().qknorm_rope_kvwrite(qkv, nH, nKV, D, qw, kw, eps, cos, sin, rot, positions, seq, table, kp, vp, True, status,
+                                    interleaved=interleaved)
     assert int(status.item()) == 0
 
     def plain(x, w):
@@ -289,8 +291,13 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
             x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
         if rot:
             c, s = cos[positions.long()][:, None, :], sin[positions.long()][:, None, :]
-            x1, x2, rest = x[..., :rot // 2], x[..., rot // 2:rot], x[..., rot:]
-            x = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], -1)
+            if interleaved:
+                x1, x2, rest = x[..., 0:rot:2], x[..., 1:rot:2], x[..., rot:]
+                turned = torch.stack([x1 * c - x2 * s, x2 * c + x1 * s], -1).reshape(*x.shape[:-1], rot)
+                x = torch.cat([turned, rest], -1)
+            else:
+                x1, x2, rest = x[..., :rot // 2], x[..., rot // 2:rot], x[..., rot:]
+                x = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], -1)
         return x
     q = qkv[:, :nH * D].reshape(T, nH, D)
     k = qkv[:, nH * D:(nH + nKV) * D].reshape(T, nKV, D)
@@ -308,7 +315,7 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm):
     assert float(kp[unwritten].abs().max()) == 0 and float(vp[unwritten].abs().max()) == 0
     # q only (a layer that reads another layer's cache)
     q_only = K().qknorm_rope_kvwrite(qkv[:, :nH * D], nH, nKV, D, qw, kw, eps, cos, sin, rot, positions, None, None,
-                                     None, None, False)
+                                     None, None, False, interleaved=interleaved)
     assert torch.equal(q_only, q_out)
     # a bad page id is reported, not written
     bad = table.clone()

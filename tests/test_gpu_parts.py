@@ -429,3 +429,84 @@ def test_toy_routed_feed_forward_and_another_position_encoding(dtype):
     finally:
         unregister_part("feed_forward", "toy_routed")
         unregister_part("position", "toy_linear_angle")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_a_position_encoding_that_turns_adjacent_pairs(dtype):
+    """A position part from outside the package whose angle j turns elements 2 j and 2 j + 1 (not j and j + half):
+    it says so with ``interleaved = True`` and the attention mixer's kernel pairs accordingly.  Against a plain
+    whole-sequence computation written here, through every way of cutting."""
+    from prelude_b200.config import load_model_config
+    from prelude_b200.parts.registry import register_part, unregister_part
+    from prelude_b200.weights.random_init import random_tensors
+
+    @dataclass(frozen=True)
+    class AdjacentSpec:
+        head_dim: int
+        theta: float
+        max_positions: int
+        kind: str = "toy_adjacent_pairs"
+
+    def angles(D, n, theta):
+        inv = torch.tensor([1.0 / theta ** (i / D) for i in range(0, D, 2)], dtype=torch.float64).float()
+        return torch.arange(n, dtype=torch.float32)[:, None] * inv[None]
+
+    @register_part("position", "toy_adjacent_pairs")
+    class AdjacentPairs:
+        interleaved = True
+
+        def __init__(self, spec, prefix=""):
+            self.spec = spec
+            self.cos = self.sin = None
+
+        def tensors(self):
+            return {}
+
+        def load(self, get, ctx):
+            ang = angles(self.spec.head_dim, self.spec.max_positions, self.spec.theta)
+            self.cos, self.sin = ang.cos().contiguous().to(ctx.device), ang.sin().contiguous().to(ctx.device)
+
+        @property
+        def rotary_dim(self):
+            return self.spec.head_dim
+
+    try:
+        cfg, init, page = tiny.PARAMS["B"]
+        D, nH, nKV, eps = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["rms_norm_eps"]
+        spec = load_model_config(cfg).to_model_spec()
+        pos = AdjacentSpec(D, 5000.0, cfg["max_position_embeddings"])
+        spec = replace(spec, blocks=tuple(replace(b, mixer=replace(b.mixer, position=pos)) for b in spec.blocks))
+        w = {k: v.to(dtype) for k, v in random_tensors(cfg, **init).items()}
+        wf = {k: v.float() for k, v in w.items()}
+
+        def plain_logits(ids):
+            L = len(ids)
+            ang = angles(D, L, 5000.0)
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+            def turn(x):                                                    # [L, heads, D], pairs (2j, 2j + 1)
+                a, b = x[..., 0::2], x[..., 1::2]
+                return torch.stack([a * cos - b * sin, b * cos + a * sin], -1).reshape(x.shape)
+
+            res = plain.embedding(torch.tensor(ids), wf["model.embed_tokens.weight"])
+            for i in range(cfg["num_hidden_layers"]):
+                p = f"model.layers.{i}"
+                x = plain.rms_norm(res, wf[f"{p}.input_layernorm.weight"], eps)
+                q = plain.rms_norm((x @ wf[f"{p}.self_attn.q_proj.weight"].T).reshape(L, nH, D), wf[f"{p}.self_attn.q_norm.weight"], eps)
+                k = plain.rms_norm((x @ wf[f"{p}.self_attn.k_proj.weight"].T).reshape(L, nKV, D), wf[f"{p}.self_attn.k_norm.weight"], eps)
+                v = (x @ wf[f"{p}.self_attn.v_proj.weight"].T).reshape(L, nKV, D)
+                o = plain.causal_attention(turn(q), turn(k), v, 1.0 / math.sqrt(D))
+                res = res + o.reshape(L, nH * D) @ wf[f"{p}.self_attn.o_proj.weight"].T
+                res = res + plain.swiglu_mlp(plain.rms_norm(res, wf[f"{p}.post_attention_layernorm.weight"], eps), wf, f"{p}.mlp")
+            return plain.rms_norm(res, wf["model.norm.weight"], eps) @ wf["lm_head.weight"].T
+
+        reqs = {"x": tiny.random_ids(41, cfg["vocab_size"], 61), "y": tiny.random_ids(19, cfg["vocab_size"], 62)}
+        ref = {rid: plain_logits(toks) for rid, toks in reqs.items()}
+        half_split = plain.forward_logits(dict(cfg, rope_theta=5000.0), wf, reqs["x"])
+        assert (ref["x"][-1] - half_split[-1]).abs().max() > 1e-3          # the pairing matters
+        for got in _run_model(spec, w, dtype, reqs, page):
+            for (rid, p), row in got.items():
+                want = ref[rid][p]
+                assert (row - want).abs().max() <= (2e-4 if dtype == torch.float32 else 4e-2 * float(want.abs().max()))
+    finally:
+        unregister_part("position", "toy_adjacent_pairs")
