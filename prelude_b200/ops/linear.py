@@ -8,8 +8,13 @@ bfloat16, float32 accumulation:
   * up to 16 rows (decode steps): the weight-streaming kernel of this library
     (bulk copies into a shared-memory ring that start before the previous kernel
     has finished, mma.sync, every block owning whole output features);
-  * cuBLAS through torch.mm above 16 rows, which is where the reference's own
-    dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433).
+  * the merged gate/up projection of a prompt step (from ``PAIR_MIN_ROWS`` rows): the paired-block tcgen05
+    kernel of this library with silu(gate) * up in its epilogue (measured on B200 at 2,048 x 19,456 x 2,560:
+    135 us against 159 us for cuBLAS followed by the activation kernel);
+  * cuBLAS through torch.mm for the other products above 16 rows, which is where the reference's own
+    dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433); PRELUDE_PREFILL_GEMM=pair
+    sends them to the paired-block kernel too (on a par at 2,048 rows and more where the tiles fill the
+    multiprocessors' waves, slower where they do not), =cublas none.
 """
 from __future__ import annotations
 
@@ -25,6 +30,12 @@ from .library import KernelLibraryError, check
 
 # rows up to which the streaming kernel is used (0 turns it off; it takes 16 at most)
 STREAM_MAX_ROWS = int(os.environ.get("PRELUDE_STREAM_MAX_ROWS", "16"))
+# which products of prompt steps run on the paired-block tcgen05 kernel: "auto" the gated one, "pair" all, "cublas" none
+PREFILL_GEMM = os.environ.get("PRELUDE_PREFILL_GEMM", "auto")
+if PREFILL_GEMM not in ("auto", "pair", "cublas"):
+    raise KernelLibraryError(f"PRELUDE_PREFILL_GEMM={PREFILL_GEMM!r} is not auto, pair or cublas")
+# rows from which they do (below, a 256-row tile is mostly empty or the tiles are too few for the device)
+PAIR_MIN_ROWS = int(os.environ.get("PRELUDE_PAIR_MIN_ROWS", "768"))
 
 
 def stream_takes(x: torch.Tensor, weight: torch.Tensor, splits: int = 1) -> bool:
@@ -63,12 +74,41 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
 
 
 def gated_linear_silu(x: torch.Tensor, weight_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
-    """silu(x Wg^T) * (x Wu^T) for the merged [gate; up] weight in one kernel, where the streaming
-    kernel takes the shape (a decode step); None otherwise - the caller then multiplies and
-    activates in two steps."""
-    if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and stream_takes(x, weight_gate_up):
-        return gemm_stream(x, weight_gate_up, gated=True)
+    """silu(x Wg^T) * (x Wu^T) for the merged [gate; up] weight in one kernel: the streaming kernel where it
+    takes the shape (a decode step), the paired-block kernel for the many rows of a prompt step; None
+    otherwise - the caller then multiplies and activates in two steps."""
+    if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16:
+        if stream_takes(x, weight_gate_up):
+            return gemm_stream(x, weight_gate_up, gated=True)
+        if PREFILL_GEMM != "cublas" and x.shape[0] >= PAIR_MIN_ROWS and pair_takes(x, weight_gate_up, gated=True):
+            return gemm_pair(x, weight_gate_up, gated=True)
     return None
+
+
+def pair_takes(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> bool:
+    """Whether the paired-block tcgen05 kernel takes x [M, K] against weight [N, K]."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and bool(_l.library().pb_gemm_pair_supported(x.shape[0], weight.shape[0], x.shape[1], x.stride(0),
+                                                         weight.stride(0), 1 if gated else 0)))
+
+
+def gemm_pair(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, gated: bool = False,
+              out: Optional[torch.Tensor] = None, max_pairs: int = 0) -> torch.Tensor:
+    """The product on paired blocks of the fifth-generation tensor cores (prompt steps); bfloat16 out.
+    With ``gated``, weight is [2 N, K] (N gate rows, then N up rows) and the result is silu(gate) * up, [M, N].
+    ``max_pairs`` (tests): fewer pairs of blocks than the device has."""
+    M, Kdim = x.shape
+    N = weight.shape[0] // 2 if gated else weight.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise KernelLibraryError("gemm_pair: out must be bfloat16 [M, N] with dense rows")
+    check(_l.library().pb_gemm_pair_bf16(
+        x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), M, weight.shape[0],
+        Kdim, x.stride(0), weight.stride(0), out.stride(0), 1 if gated else 0, 1, max_pairs,
+        tc_status(x.device).data_ptr(), _l.current_stream_ptr(x.device)), "gemm_pair")
+    return out
 
 
 _tc_status: Dict[torch.device, torch.Tensor] = {}
@@ -126,6 +166,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             return K.PartialSums(gemm_stream(x, weight, bias, out_dtype, splits=splits))
         if stream_takes(x, weight):
             return gemm_stream(x, weight, bias, out_dtype)
+        if PREFILL_GEMM == "pair" and out_dtype == torch.bfloat16 and x.shape[0] >= PAIR_MIN_ROWS and pair_takes(x, weight):
+            return gemm_pair(x, weight, bias)
         if out_dtype == torch.bfloat16:
             y = torch.mm(x, weight.t())
         else:

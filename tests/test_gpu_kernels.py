@@ -622,6 +622,81 @@ def test_gemm_stream_gated(M, I, K_):
     assert gated_linear_silu(rnd(40, K_, dtype=torch.bfloat16), w) is None      # too many rows: the caller takes two steps
 
 
+# ---------------------------------------------------------------------------------------
+# the paired-block tcgen05 product for prompt steps
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K_", [(2048, 2560, 4096), (1024, 6144, 2560), (256, 256, 64), (300, 520, 328), (77, 1000, 72),
+                                    (515, 264, 2056), (1, 8, 8), (1000, 40003, 96)])
+@pytest.mark.parametrize("max_pairs", [0, 3])
+def test_gemm_pair(M, N, K_, max_pairs):
+    # tiles that end inside the matrix in every direction, one pair that walks many tiles, more pairs than tiles
+    from prelude_b200.ops.linear import gemm_pair, pair_takes, tc_status
+    x, w, b = rnd(M, K_, dtype=torch.bfloat16, seed=41), rnd(N, K_, dtype=torch.bfloat16, seed=42, scale=0.05), rnd(N, seed=43)
+    assert pair_takes(x, w)
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    got = gemm_pair(x, w, max_pairs=max_pairs)
+    assert got.shape == (M, N) and got.dtype == torch.bfloat16
+    assert (got.double() - want).abs().max() <= tol(torch.bfloat16, scale)
+    assert torch.equal(gemm_pair(x, w, max_pairs=max_pairs), got)
+    assert torch.equal(gemm_pair(x, w, max_pairs=5), got)                 # who computes a tile does not change it
+    with_bias = gemm_pair(x, w, b, max_pairs=max_pairs)
+    assert (with_bias.double() - (want + b.double())).abs().max() <= tol(torch.bfloat16, scale + float(b.abs().max()))
+    if M > 1:           # a row does not depend on the rows beside it
+        assert torch.equal(gemm_pair(x[M - 1:M].contiguous(), w), got[M - 1:M])
+    wide = rnd(M, K_ + 64, dtype=torch.bfloat16, seed=44)                  # x and the result as views into wider tensors
+    out = torch.full((M, N + 24), 7.0, dtype=torch.bfloat16, device="cuda")
+    gemm_pair(wide[:, 32:32 + K_], w, out=out[:, 8:8 + N])
+    assert torch.equal(out[:, 8:8 + N], gemm_pair(wide[:, 32:32 + K_].contiguous(), w))
+    assert bool((out[:, :8] == 7).all()) and bool((out[:, 8 + N:] == 7).all())
+    assert int(tc_status(x.device).item()) == 0
+
+
+@pytest.mark.parametrize("M,I,K_", [(2048, 9728, 2560), (768, 1000, 264), (256, 128, 64), (300, 77, 96), (5, 8, 32), (1030, 200, 1504)])
+def test_gemm_pair_gated(M, I, K_):
+    # silu(x Wg^T) * (x Wu^T) from the merged weight, against the two-step computation in float64
+    from prelude_b200.ops.linear import PAIR_MIN_ROWS, gated_linear_silu, gemm_pair, tc_status
+    x, w = rnd(M, K_, dtype=torch.bfloat16, seed=51), rnd(2 * I, K_, dtype=torch.bfloat16, seed=52, scale=0.05)
+    g, u = x.double() @ w[:I].double().T, x.double() @ w[I:].double().T
+    want = g / (1 + torch.exp(-g)) * u
+    got = gemm_pair(x, w, gated=True)
+    assert got.shape == (M, I) and got.dtype == torch.bfloat16
+    assert (got.double() - want).abs().max() <= tol(torch.bfloat16, float(want.abs().max()))
+    assert torch.equal(gemm_pair(x, w, gated=True, max_pairs=2), got)
+    if M >= PAIR_MIN_ROWS:
+        assert torch.equal(gated_linear_silu(x, w), got)                  # a prompt step's projection goes this way
+    assert int(tc_status(x.device).item()) == 0
+
+
+def test_gemm_pair_finds_the_one_weight_that_matters():
+    # one large product at chosen places of M, N and K, everything else small: a lost stage, row or column shows
+    from prelude_b200.ops.linear import gemm_pair
+    M, N, K_ = 700, 1300, 1096
+    x, w = rnd(M, K_, dtype=torch.bfloat16, seed=1, scale=0.01), rnd(N, K_, dtype=torch.bfloat16, seed=2, scale=0.01)
+    for (m, n, k) in [(0, 0, 0), (M - 1, N - 1, K_ - 1), (127, 127, 63), (128, 128, 64), (255, 255, 383), (256, 256, 384),
+                      (511, 1279, 1087), (640, 1280, 1088), (129, 383, 447), (383, 129, 448)]:
+        x2, w2 = x.clone(), w.clone()
+        x2[m, k], w2[n, k] = 8.0, 8.0
+        got = gemm_pair(x2, w2, max_pairs=4)
+        assert abs(float(got[m, n]) - 64.0) < 1.0
+        got[m, n] = 0
+        assert float(got.abs().max()) < 1.0
+
+
+def test_gemm_pair_refuses_other_shapes_and_linear_goes_on():
+    from prelude_b200.ops.library import KernelLibraryError
+    from prelude_b200.ops.linear import gemm_pair, linear, pair_takes
+    x, w = rnd(300, 68, dtype=torch.bfloat16), rnd(40, 68, dtype=torch.bfloat16)      # rows of 136 bytes: no tensor map
+    assert not pair_takes(x, w)
+    with pytest.raises(KernelLibraryError, match="not taken"):
+        gemm_pair(x, w)
+    want = x.double() @ w.double().T
+    assert (linear(x, w).double() - want).abs().max() <= tol(torch.bfloat16, float(want.abs().max()))
+    assert not pair_takes(rnd(300, 64, dtype=torch.bfloat16), rnd(41, 64, dtype=torch.bfloat16), gated=True)   # gate rows != up rows
+    with pytest.raises(KernelLibraryError, match="no bias"):
+        gemm_pair(rnd(300, 64, dtype=torch.bfloat16), rnd(40, 64, dtype=torch.bfloat16), rnd(20), gated=True)
+
+
 def test_gemm_stream_finds_the_one_weight_that_matters():
     # one large product at the far end of K and of N, everything else small: a lost chunk or row shows
     from prelude_b200.ops.linear import gemm_stream

@@ -5,7 +5,8 @@ Qwen3-8B (1 of 36 layers) and Qwen3-32B (1 of 64 layers; the last two with a voc
 two and no multiple of eight), so that the kernels' paths for these widths run inside a model: pages with
 permuted chunks, bulk-copy decode attention with its keys split over blocks and merged, the tcgen05 prompt
 attention behind a cached prefix, the streaming product with the output head's 151,936 rows, the down
-projection as four partial sums, the library product above 16 rows.
+projection as four partial sums, the library product above 16 rows, the paired-block tcgen05 product with the
+activation in its epilogue for a long prompt's gate/up projection.
 
 Weights are drawn on the GPU and rounded to bfloat16 once; the 32-bit run, the bfloat16 run and the plain
 implementation all use those same values, so no difference comes from the weights.
@@ -116,7 +117,10 @@ def _check(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("name", ["4b", "8b", "32b"])
-def test_every_way_of_cutting_at_real_layer_sizes(name):
+def test_every_way_of_cutting_at_real_layer_sizes(name, monkeypatch):
+    from prelude_b200.ops import linear as LN
+    pair_rows, pair = [], LN.gemm_pair
+    monkeypatch.setattr(LN, "gemm_pair", lambda x, *a, **k: (pair_rows.append(x.shape[0]), pair(x, *a, **k))[1])
     s = _sized(name)
     V = s.cfg["vocab_size"]
     if name == "4b":
@@ -150,6 +154,8 @@ def test_every_way_of_cutting_at_real_layer_sizes(name):
             del runner
         del s._models[dtype]
         torch.cuda.empty_cache()
+    if name == "4b":        # the 790-token prompt's gate/up projection went through the paired-block tcgen05 kernel
+        assert pair_rows and max(pair_rows) >= LN.PAIR_MIN_ROWS
 
 
 @pytest.mark.parametrize("batch", [1, 8, 17])
