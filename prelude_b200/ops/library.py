@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 14
+ABI_VERSION = 15
 
 
 class KernelLibraryError(RuntimeError):
@@ -31,6 +31,7 @@ _SIGNATURES = {
     "pb_rmsnorm": ([P, P, P, I, I, I, F, P], I),
     "pb_gather_add_rmsnorm": ([P, I, L, P, P, P, P, I, I, I, I, F, P], I),
     "pb_qknorm_rope_kvwrite": ([P, P, P, L, P, P, P, I, P, P, F, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, P, P], I),
+    "pb_rope_set_heads_min_tokens": ([I], I),
     "pb_paged_attention_ref": ([P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
     "pb_silu_mul": ([P, P, I, I, I, P], I),
     "pb_gemm_ref": ([P, P, P, P, I, I, I, I, I, L, L, L, P], I),

@@ -324,6 +324,65 @@ def test_qknorm_rope_kvwrite(dtype, nH, nKV, D, rot, norm, interleaved):
     assert int(status.item()) != 0
 
 
+@pytest.mark.parametrize("nH,nKV,D,rot", [(32, 8, 128, 128), (6, 2, 64, 64), (9, 3, 128, 64), (7, 1, 64, 32), (8, 4, 128, 0)])
+@pytest.mark.parametrize("norm,interleaved", [(True, False), (False, False), (True, True)])
+def test_qknorm_rope_kvwrite_many_tokens(nH, nKV, D, rot, norm, interleaved):
+    # A prompt step's rows go through the form of the kernel that takes eight heads of a token together (groups
+    # that hold queries and keys, keys and values, or run past the last head); the same rows in portions of fewer
+    # than 256 tokens, and whole with that form switched off, go through the one-head form, which the test above
+    # holds against the formulas: all must agree bit for bit, padding rows of a captured step and a bad page included.
+    T, page, eps, theta = 700, 16, 1e-6, 10000.0
+    dtype = torch.bfloat16
+    qkv = rnd(T, (nH + 2 * nKV) * D + 8, dtype=dtype, seed=5)[:, 8:]            # rows of a wider tensor
+    qw, kw = (1 + 0.2 * rnd(D, seed=2), 1 + 0.2 * rnd(D, seed=3)) if norm else (None, None)
+    cos = sin = None
+    if rot:
+        inv = torch.tensor([1.0 / theta ** (i / rot) for i in range(0, rot, 2)], dtype=torch.float64).float()
+        ang = torch.arange(512, dtype=torch.float32)[:, None] * inv[None]
+        cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    # three requests of 300, 250 and 140 tokens and ten padding rows; pages dealt out in a scrambled order
+    lens = [300, 250, 140]
+    pos = torch.cat([torch.arange(n) for n in lens] + [torch.zeros(10, dtype=torch.long)]).to(torch.int32).to(DEV)
+    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)] + [torch.full((10,), -1)]).to(torch.int32).to(DEV)
+    per = -(-max(lens) // page)
+    perm = torch.randperm(3 * per + 5, generator=torch.Generator().manual_seed(9)).to(torch.int32)
+    table = perm[:3 * per].reshape(3, per).to(DEV)
+    num_pages = 3 * per + 5
+
+    def run(rows, table_):
+        kp = torch.zeros(num_pages, nKV, page, D, dtype=dtype, device=DEV)
+        vp = torch.zeros_like(kp)
+        st = torch.zeros(1, dtype=torch.int32, device=DEV)
+        outs = []
+        for a, b in rows:
+            outs.append(K().qknorm_rope_kvwrite(qkv[a:b], nH, nKV, D, qw, kw, eps, cos, sin, rot, pos[a:b], seq[a:b], table_, kp, vp,
+                                                True, st, interleaved=interleaved))
+        return torch.cat(outs), kp, vp, int(st.item())
+
+    from prelude_b200.ops.library import library
+    whole = run([(0, T)], table)
+    parts = run([(a, min(a + 200, T)) for a in range(0, T, 200)], table)
+    before = library().pb_rope_set_heads_min_tokens(1 << 30)
+    try:
+        one_head = run([(0, T)], table)
+    finally:
+        library().pb_rope_set_heads_min_tokens(before)
+    assert whole[3] == 0 and parts[3] == 0 and one_head[3] == 0
+    assert torch.equal(whole[1], one_head[1]) and torch.equal(whole[2], one_head[2])
+    live = (seq >= 0)
+    assert torch.equal(whole[0][live], parts[0][live]) and torch.equal(whole[0][live], one_head[0][live])
+    assert torch.equal(whole[1], parts[1]) and torch.equal(whole[2], parts[2])
+    assert float(whole[1].abs().max()) > 0 and float(whole[2].abs().max()) > 0
+    q_only = K().qknorm_rope_kvwrite(qkv[:, :nH * D], nH, nKV, D, qw, kw, eps, cos, sin, rot, pos, None, None, None, None, False,
+                                     interleaved=interleaved)
+    assert torch.equal(q_only[live], whole[0][live])
+    bad = table.clone()
+    bad[1, 3] = num_pages + 7                                                    # request 1, positions 48..63
+    wb, pb_ = run([(0, T)], bad), run([(a, min(a + 200, T)) for a in range(0, T, 200)], bad)
+    assert wb[3] == 2 and pb_[3] == 2
+    assert torch.equal(wb[1], pb_[1]) and torch.equal(wb[2], pb_[2]) and torch.equal(wb[0][live], pb_[0][live])
+
+
 def test_kernels_refuse_what_they_cannot_do():
     from prelude_b200.ops.library import KernelLibraryError
     q = rnd(1, 2, 272)
