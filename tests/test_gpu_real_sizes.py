@@ -135,6 +135,8 @@ def test_every_way_of_cutting_at_real_layer_sizes(name, monkeypatch):
     plain32 = float((forward_logits(s.cfg, w32, reqs[longest]).double() - ref[longest]).abs().max())
     del s._w[torch.float32]
     scheds = _schedules(reqs)
+    if name == "4b":        # a captured prompt step long enough for the paired-block product (and a two-token rest behind it)
+        scheds["long_portions"] = harness.portions(reqs, sizes=(788, 2))
     total = sum(-(-len(t) // PAGE) for t in reqs.values())
     for dtype in (torch.float32, torch.bfloat16):
         model = s.model(dtype)
@@ -142,11 +144,14 @@ def test_every_way_of_cutting_at_real_layer_sizes(name, monkeypatch):
             num_pages = harness.peak_tokens(schedule, PAGE) // PAGE
             if cut == "mixed":
                 assert num_pages < total                     # the pool forces pages to be used again
-            runner = _runner(model, num_pages, max_request_tokens=1024 if cut in ("portions", "mixed") else None)
-            if cut in ("portions", "mixed"):
+            runner = _runner(model, num_pages, max_request_tokens=1024 if cut != "whole" and cut != "tail_decode" else None)
+            if cut in ("portions", "mixed", "long_portions"):
                 runner.enable_step_graphs()                  # the captured prompt steps that the entry point uses
+            calls = len(pair_rows)
             got = harness.run_schedule(runner, schedule)
             assert len(got) == sum(len(t) for t in reqs.values())
+            if cut == "long_portions" and dtype == torch.bfloat16:
+                assert len(pair_rows) > calls             # captured with the paired-block product inside
             worst = _check(got, ref, dtype, f"{name} {cut}")
             print(f"{name} {str(dtype)[6:]} {cut}: worst {worst[0]:.3e} (rms {worst[1]:.3e}); plain 32-bit is {plain32:.3e} from float64")
             runner.cache.check()
