@@ -80,18 +80,45 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
     PB_TL(PB_TL_NORM, PB_TL_AFTER_WAIT);
     float4 keep[ITERS];
     float ss = 0.f;
+    // Every load of the row is issued before the first sum (up to four parts): the kernel is one round trip to
+    // the L2 cache, a reduction and a store, and with the loads of one iteration behind the store of the one
+    // before it was three round trips (4.1 us for 8 rows of 2,560 in a decode step).
+    float4 part[ITERS][4];
+    uint2 raw[ITERS];
+    const bool ahead = x != nullptr && (sizeof(TX) == 2 || n_parts <= 4);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
         int i = threadIdx.x + it * blockDim.x;
         if (i < n4) {
-            float4 v = r4[i];
+            keep[it] = r4[i];
+            if (ahead) {
+                const TX* xr = x + row * width + 4 * (size_t)i;
+                if constexpr (sizeof(TX) == 2) {
+                    raw[it] = *reinterpret_cast<const uint2*>(xr);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        part[it][u] = (u < n_parts) ? *reinterpret_cast<const float4*>(xr + (size_t)u * part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            float4 v = keep[it];
             if (x != nullptr) {
                 const TX* xr = x + row * width + 4 * (size_t)i;
                 if constexpr (sizeof(TX) == 2) {
-                    uint2 raw = *reinterpret_cast<const uint2*>(xr);
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[it]);
                     float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
                     v.x += a.x; v.y += a.y; v.z += b.x; v.w += b.y;
+                } else if (ahead) {
+                    // the parts in ascending order
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (u < n_parts) { v.x += part[it][u].x; v.y += part[it][u].y; v.z += part[it][u].z; v.w += part[it][u].w; }
                 } else {
                     // the parts in ascending order, four loads in flight at a time
                     for (int s0 = 0; s0 < n_parts; s0 += 4) {
