@@ -27,7 +27,7 @@ bool pb_pdl_enabled() {
 PB_API const char* pb_last_error() { return g_pb_error; }
 
 // Interface version: the Python side refuses a library built from other sources.
-PB_API int pb_abi_version() { return 15; }
+PB_API int pb_abi_version() { return 16; }
 
 // Compute capability the library was compiled for (major*10 + minor).
 PB_API int pb_built_for_sm() { return 100; }

@@ -19,6 +19,12 @@
 // accumulator are gate sums and 128..255 the up sums of those features, and the epilogue writes silu(gate) * up:
 // the activation costs no kernel and the 2N-wide intermediate never exists.
 //
+// The q/k/v form serves the merged projection of an attention layer whose heads are 64, 128 or 256 wide: a tile
+// holds whole heads and a thread a whole row of each, so the epilogue does what otherwise a kernel of its own does
+// after the product - the per-head RMSNorm of queries and keys, the rotation by the token's position (the pair
+// (j, j + head/2)), queries to their dense tensor and keys and values into the token's place in the cache pages -
+// from the float32 sums, without the merged projection ever being written or read.
+//
 // Work.  Persistent pairs: pair p of P takes tiles p, p + P, ...; tiles run down the rows of A first, so that the
 // pairs of a wave share a panel of B in the L2 cache.  (Dealing the last wave out in units of (tile, 64 of K), with
 // the parts of a split tile summed through the L2 cache, was measured: the products are bound by power here, not by
@@ -43,7 +49,25 @@ namespace cg = cooperative_groups;
 #define GP_A_BYTES (GP_BM * GP_BK * 2)              // a stage's tile of A in one block
 #define GP_STAGE_BYTES (2 * GP_A_BYTES)             // and as much of B
 
+// What the q/k/v form needs beside the product (the arguments of the norm/rotary/cache-write kernel).
+struct GpHeads {
+    __nv_bfloat16* q_out;           // [tokens, n_heads, head_dim]
+    __nv_bfloat16* k_pages;         // [pages, n_kv_heads, page_size, head_dim]
+    __nv_bfloat16* v_pages;
+    const float* q_weight;          // per-head norm scales, or null
+    const float* k_weight;
+    const float* cos_table;         // [max_positions, head_dim / 2]
+    const float* sin_table;
+    const int32_t* positions;
+    const int32_t* token_seq;       // row of the block table per token; negative: a padding row
+    const int32_t* block_table;
+    float eps;
+    int max_positions, table_stride, page_size, num_pages;
+    int n_heads, n_kv_heads, head_dim, swizzle;
+};
+
 struct GpParams {
+    GpHeads heads;
     __nv_bfloat16* out;             // [rows_a, out_cols]
     const float* bias;              // per output column, or null
     int* status;
@@ -51,7 +75,7 @@ struct GpParams {
     int rows_a, rows_b, K;          // rows_b: rows of B (2 * out_cols when gated)
     int out_cols;
     int tiles_m, tiles_n, kblocks;
-    int gated;
+    int gated;                      // 0: plain; 1: silu(gate) * up; 2: q/k/v heads
     int b_is_constant;
 };
 
@@ -120,6 +144,122 @@ __device__ __forceinline__ void gp_store_chunk(__nv_bfloat16* dst, const float* 
     }
 }
 
+// 32 values to bfloat16 as four 16-byte chunks of a head's row, chunk c of the row at position c ^ flip (the pages'
+// permutation; 0 for none)
+__device__ __forceinline__ void gp_store_head_chunks(__nv_bfloat16* row, int col, const float* v, int flip) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        unsigned w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]);
+            w[j] = *reinterpret_cast<unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(row + (((col >> 3) + q) ^ flip) * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// The epilogue of the q/k/v form for one tile: this thread's token, the 256 / head_dim heads of the tile.
+// (Norm, rotation and the cache write as crates/prelude-core/src/models/qwen3.rs:161-231 orders them; the same
+// arithmetic as the kernel in rope_kv.cu, on the float32 sums instead of their bfloat16 rounding.)
+__device__ __forceinline__ void gp_heads_epilogue(const GpParams& p, uint32_t taddr, int tn, int t, bool live) {
+    const GpHeads& r = p.heads;
+    const int D = r.head_dim, half = D >> 1;
+    const int pos = live ? r.positions[t] : 0;
+    const int seq = (live && r.token_seq) ? r.token_seq[t] : 0;
+    const bool padding = seq < 0;
+    const bool pos_ok = pos >= 0 && pos < r.max_positions;
+    bool page_known = false, page_ok = false;
+    size_t page_row = 0;
+    int in_page = 0;
+    const int heads_per_tile = GP_BN / D, total_heads = r.n_heads + 2 * r.n_kv_heads;
+    for (int hh = 0; hh < heads_per_tile; ++hh) {
+        const int slot = tn * heads_per_tile + hh;
+        if (slot >= total_heads) break;                                     // the same for the whole block
+        const bool is_q = slot < r.n_heads, is_k = !is_q && slot < r.n_heads + r.n_kv_heads;
+        const int h = is_q ? slot : (is_k ? slot - r.n_heads : slot - r.n_heads - r.n_kv_heads);
+        const uint32_t tcol = taddr + hh * D;
+        bool store = live && !padding;
+        __nv_bfloat16* dst = nullptr;
+        int flip = 0;
+        if (is_q) {
+            dst = r.q_out + ((size_t)t * r.n_heads + h) * D;
+        } else {
+            if (!page_known && store) {                                     // the token's place in the cache, once
+                page_known = true;
+                const int page = pos >= 0 ? r.block_table[(size_t)seq * r.table_stride + pos / r.page_size] : -1;
+                if (page < 0 || page >= r.num_pages) {
+                    if (p.status) atomicExch(p.status, 2);
+                } else {
+                    page_ok = true;
+                    in_page = pos % r.page_size;
+                    page_row = (size_t)page * r.n_kv_heads;
+                }
+            }
+            store = store && page_ok;
+            dst = (is_k ? r.k_pages : r.v_pages) + ((page_row + h) * r.page_size + in_page) * D;
+            flip = r.swizzle ? (in_page & 7) : 0;
+        }
+        if (!is_q && !is_k) {                                               // values: as they are
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float v[32];
+                gp_row_chunk(tcol + c0, v);
+                if (store) gp_store_head_chunks(dst, c0, v, flip);
+            }
+            continue;
+        }
+        const float* weight = is_q ? r.q_weight : r.k_weight;
+        float inv = 1.0f;
+        if (weight != nullptr) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float v[32];
+                gp_row_chunk(tcol + c0, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ss += v[j] * v[j];
+            }
+            inv = 1.0f / sqrtf(ss / (float)D + r.eps);
+        }
+        if (store && !pos_ok) {
+            if (p.status) atomicExch(p.status, 3);
+            store = false;
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < half; c0 += 32) {
+            float a[32], b[32];
+            gp_row_chunk(tcol + c0, a);
+            gp_row_chunk(tcol + half + c0, b);
+            if (store) {
+                if (weight != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 wa = *reinterpret_cast<const float4*>(weight + c0 + j), wb = *reinterpret_cast<const float4*>(weight + half + c0 + j);
+                        a[j] *= inv * wa.x; a[j + 1] *= inv * wa.y; a[j + 2] *= inv * wa.z; a[j + 3] *= inv * wa.w;
+                        b[j] *= inv * wb.x; b[j + 1] *= inv * wb.y; b[j + 2] *= inv * wb.z; b[j + 3] *= inv * wb.w;
+                    }
+                }
+                const float4* cs = reinterpret_cast<const float4*>(r.cos_table + (size_t)pos * half + c0);
+                const float4* sn = reinterpret_cast<const float4*>(r.sin_table + (size_t)pos * half + c0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 c = cs[j], s = sn[j];
+                    const float cc[4] = {c.x, c.y, c.z, c.w}, ss4[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float x = a[4 * j + u], y = b[4 * j + u];
+                        a[4 * j + u] = x * cc[u] - y * ss4[u];
+                        b[4 * j + u] = y * cc[u] + x * ss4[u];
+                    }
+                }
+                gp_store_head_chunks(dst, c0, a, flip);
+                gp_store_head_chunks(dst, half + c0, b, flip);
+            }
+        }
+    }
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GpParams p) {
     pb_grid_dep_launch();
@@ -158,7 +298,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int a_row = tm * 256 + rank * GP_BM;
-                const int b_row = p.gated ? (rank == 0 ? tn * GP_HALF : p.out_cols + tn * GP_HALF) : tn * GP_BN + rank * GP_HALF;
+                const int b_row = p.gated == 1 ? (rank == 0 ? tn * GP_HALF : p.out_cols + tn * GP_HALF) : tn * GP_BN + rank * GP_HALF;
                 for (int kb = 0; kb < p.kblocks; ++kb, ++fill) {
                     const int stage = fill % GP_STAGES;
                     ok = tc_mbar_wait(&empty_bar[stage], ((fill / GP_STAGES) & 1) ^ 1);
@@ -223,7 +363,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int gi = tm * 256 + rank * GP_BM + row;
             const bool live = gi < p.rows_a;
             __nv_bfloat16* orow = p.out + (size_t)(live ? gi : 0) * p.ldo;
-            if (p.gated) {
+            if (p.gated == 2) {
+                gp_heads_epilogue(p, taddr, tn, gi, live);
+            } else if (p.gated) {
                 const int col0 = tn * GP_HALF;
 #pragma unroll 1
                 for (int c0 = 0; c0 < GP_HALF; c0 += 32) {
@@ -295,6 +437,27 @@ static int gp_max_pairs() {
     return pairs;
 }
 
+static int gp_launch(const void* A, const void* B, long long lda, long long ldb, GpParams& p, int max_pairs, cudaStream_t stream) {
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    PB_REQUIRE(tiles < (1ll << 30), "gemm_pair: %lld tiles are too many", tiles);
+    long long pairs = gp_max_pairs();
+    if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
+    if (tiles < pairs) pairs = tiles;
+    CUtensorMap ma, mb;
+    if (int e = gp_make_map(&ma, A, p.rows_a, p.K, lda)) return e;
+    if (int e = gp_make_map(&mb, B, p.rows_b, p.K, ldb)) return e;
+    const size_t smem = (size_t)GP_STAGES * GP_STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return pb_fail("gemm_pair: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    pb_launch(gemm_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(GP_THREADS), smem, stream, ma, mb, p);
+    PB_CHECK_LAUNCH("gemm_pair");
+    return 0;
+}
+
 // Whether the kernel takes the shape: 16-byte aligned rows (K and the strides multiples of 8 elements); the gated
 // form needs an even number of rows of B.
 PB_API int pb_gemm_pair_supported(int rows_a, int rows_b, int K, long long lda, long long ldb, int gated) {
@@ -321,22 +484,48 @@ PB_API int pb_gemm_pair_bf16(const void* A, const void* B, const float* bias, vo
     p.tiles_m = (rows_a + 255) / 256;
     p.tiles_n = gated ? (p.out_cols + GP_HALF - 1) / GP_HALF : (p.out_cols + GP_BN - 1) / GP_BN;
     p.kblocks = (K + GP_BK - 1) / GP_BK;
-    const long long tiles = (long long)p.tiles_m * p.tiles_n;
-    PB_REQUIRE(tiles < (1ll << 30), "gemm_pair: %lld tiles are too many", tiles);
-    long long pairs = gp_max_pairs();
-    if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
-    if (tiles < pairs) pairs = tiles;
-    CUtensorMap ma, mb;
-    if (int e = gp_make_map(&ma, A, rows_a, K, lda)) return e;
-    if (int e = gp_make_map(&mb, B, rows_b, K, ldb)) return e;
-    const size_t smem = (size_t)GP_STAGES * GP_STAGE_BYTES + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return pb_fail("gemm_pair: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
-    }
-    pb_launch(gemm_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(GP_THREADS), smem, stream, ma, mb, p);
-    PB_CHECK_LAUNCH("gemm_pair");
-    return 0;
+    return gp_launch(A, B, lda, ldb, p, max_pairs, stream);
+}
+
+// Whether the q/k/v form takes the layer: heads of 64, 128 or 256, rotation of the whole head by halves.
+PB_API int pb_gemm_pair_heads_supported(int rows_a, int K, long long lda, long long ldb, int n_heads, int n_kv_heads, int head_dim, int rotary_dim) {
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return 0;
+    if (rotary_dim != head_dim || n_heads < 1 || n_kv_heads < 0) return 0;
+    return pb_gemm_pair_supported(rows_a, (n_heads + 2 * n_kv_heads) * head_dim, K, lda, ldb, 0);
+}
+
+// x [rows_a, K] against the merged q/k/v weight [(n_heads + 2 n_kv_heads) head_dim, K]; then per head what
+// pb_qknorm_rope_kvwrite does with the projection, in the product's epilogue: queries (normalised with q_weight
+// if given, rotated) to q_out [rows_a, n_heads, head_dim], keys (k_weight) and values into the pages at
+// block_table[token_seq[t]][positions[t] / page_size].  n_kv_heads == 0: queries only (a layer that reads another
+// layer's cache).  Status 2: a token without a page; 3: a position outside the tables.
+PB_API int pb_gemm_pair_heads_bf16(const void* A, const void* B, int rows_a, int K, long long lda, long long ldb,
+                                   void* q_out, void* k_pages, void* v_pages, const float* q_weight, const float* k_weight, float eps,
+                                   const float* cos_table, const float* sin_table, int max_positions, const int32_t* positions,
+                                   const int32_t* token_seq, const int32_t* block_table, int table_stride, int page_size, int num_pages,
+                                   int n_heads, int n_kv_heads, int head_dim, int swizzle, int max_pairs, int* status, cudaStream_t stream) {
+    PB_REQUIRE(pb_gemm_pair_heads_supported(rows_a, K, lda, ldb, n_heads, n_kv_heads, head_dim, head_dim),
+               "gemm_pair: q/k/v form: rows_a=%d K=%d heads %d + 2 x %d of %d not taken", rows_a, K, n_heads, n_kv_heads, head_dim);
+    PB_REQUIRE(A && B && q_out && cos_table && sin_table && positions && pb_aligned(A, 16) && pb_aligned(B, 16) && pb_aligned(q_out, 16) &&
+               pb_aligned(cos_table, 16) && pb_aligned(sin_table, 16) && (!q_weight || pb_aligned(q_weight, 16)) && (!k_weight || pb_aligned(k_weight, 16)),
+               "gemm_pair: q/k/v form: null or unaligned pointer");
+    if (n_kv_heads > 0)
+        PB_REQUIRE(k_pages && v_pages && token_seq && block_table && page_size > 0 && num_pages > 0 && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16),
+                   "gemm_pair: q/k/v form: cache write asked for without cache arguments");
+    PB_REQUIRE(!swizzle || head_dim % 64 == 0, "gemm_pair: permuted pages have head_dim %% 64 == 0");
+    if (int e = get_encode()) return e;
+    GpParams p{};
+    p.status = status;
+    p.rows_a = rows_a; p.rows_b = (n_heads + 2 * n_kv_heads) * head_dim; p.K = K; p.gated = 2; p.b_is_constant = 1;
+    p.out_cols = p.rows_b;
+    p.tiles_m = (rows_a + 255) / 256;
+    p.tiles_n = (p.out_cols + GP_BN - 1) / GP_BN;
+    p.kblocks = (K + GP_BK - 1) / GP_BK;
+    GpHeads& r = p.heads;
+    r.q_out = (__nv_bfloat16*)q_out; r.k_pages = (__nv_bfloat16*)k_pages; r.v_pages = (__nv_bfloat16*)v_pages;
+    r.q_weight = q_weight; r.k_weight = k_weight; r.cos_table = cos_table; r.sin_table = sin_table;
+    r.positions = positions; r.token_seq = token_seq; r.block_table = block_table; r.eps = eps;
+    r.max_positions = max_positions; r.table_stride = table_stride; r.page_size = page_size; r.num_pages = num_pages;
+    r.n_heads = n_heads; r.n_kv_heads = n_kv_heads; r.head_dim = head_dim; r.swizzle = swizzle;
+    return gp_launch(A, B, lda, ldb, p, max_pairs, stream);
 }

@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 
 class KernelLibraryError(RuntimeError):
@@ -52,6 +52,8 @@ _SIGNATURES = {
     "pb_attention_decode_set_cluster": ([I], None),
     "pb_gemm_pair_supported": ([I, I, I, L, L, I], I),
     "pb_gemm_pair_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, I, P, P], I),
+    "pb_gemm_pair_heads_supported": ([I, I, L, L, I, I, I, I], I),
+    "pb_gemm_pair_heads_bf16": ([P, P, I, I, L, L, P, P, P, P, P, F, P, P, I, P, P, P, I, I, I, I, I, I, I, I, P, P], I),
     "pb_gemm_stream_supported": ([I, I, I, L, L], I),
     "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, I, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),

@@ -10,7 +10,9 @@ bfloat16, float32 accumulation:
     has finished, mma.sync, every block owning whole output features);
   * the merged gate/up projection of a prompt step (from ``PAIR_MIN_ROWS`` rows): the paired-block tcgen05
     kernel of this library with silu(gate) * up in its epilogue (measured on B200 at 2,048 x 19,456 x 2,560:
-    135 us against 159 us for cuBLAS followed by the activation kernel);
+    135 us against 159 us for cuBLAS followed by the activation kernel); the merged q/k/v projection of a long
+    prompt step (from ``PAIR_QKV_MIN_ROWS`` rows) there too, with the per-head norm, the rotation and the cache
+    write in its epilogue (``qkv_heads``);
   * cuBLAS through torch.mm for the other products above 16 rows, which is where the reference's own
     dispatch ends as well (crates/prelude-cuda/src/ops/gemm.rs:35-137, 340-433); PRELUDE_PREFILL_GEMM=pair
     sends them to the paired-block kernel too (on a par at 2,048 rows and more where the tiles fill the
@@ -36,6 +38,8 @@ if PREFILL_GEMM not in ("auto", "pair", "cublas"):
     raise KernelLibraryError(f"PRELUDE_PREFILL_GEMM={PREFILL_GEMM!r} is not auto, pair or cublas")
 # rows from which they do (below, a 256-row tile is mostly empty or the tiles are too few for the device)
 PAIR_MIN_ROWS = int(os.environ.get("PRELUDE_PAIR_MIN_ROWS", "768"))
+# rows from which the merged q/k/v projection runs there with norm, rotation and cache write in its epilogue
+PAIR_QKV_MIN_ROWS = int(os.environ.get("PRELUDE_PAIR_QKV_MIN_ROWS", "1536"))
 
 
 def stream_takes(x: torch.Tensor, weight: torch.Tensor, splits: int = 1) -> bool:
@@ -109,6 +113,52 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
         Kdim, x.stride(0), weight.stride(0), out.stride(0), 1 if gated else 0, 1, max_pairs,
         tc_status(x.device).data_ptr(), _l.current_stream_ptr(x.device)), "gemm_pair")
     return out
+
+
+def qkv_heads(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int,
+              q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+              cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+              positions: torch.Tensor, token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+              k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], write_kv: bool,
+              status: Optional[torch.Tensor], out: torch.Tensor, force: Optional[bool] = None) -> torch.Tensor:
+    """The merged q/k/v projection of x, per-head norm of queries and keys, rotation, queries to ``out``
+    [T, n_heads, head_dim] and keys and values into their pages: one paired-block product with all of it in the
+    epilogue for the many rows of a prompt step where the layer's shape allows (``force``: tests say which way),
+    else the product followed by ``kernels.qknorm_rope_kvwrite``."""
+    rows = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
+    w = w_qkv if w_qkv.shape[0] == rows else w_qkv[:rows]
+    fused = (PREFILL_GEMM != "cublas" and x.shape[0] >= PAIR_QKV_MIN_ROWS) if force is None else force
+    if (fused and bias is None and cos is not None and not interleaved and x.dtype == torch.bfloat16 and pair_takes(x, w)
+            and bool(_l.library().pb_gemm_pair_heads_supported(x.shape[0], x.shape[1], x.stride(0), w.stride(0), n_heads,
+                                                              n_kv_heads if write_kv else 0, head_dim, rotary_dim))):
+        T = x.shape[0]
+        if tuple(out.shape) != (T, n_heads, head_dim) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise KernelLibraryError(f"qkv_heads: out is {tuple(out.shape)} {out.dtype}, q is {(T, n_heads, head_dim)} bfloat16")
+        for t_, n_ in ((cos, "cos"), (sin, "sin"), (q_weight, "q_weight"), (k_weight, "k_weight")):
+            if t_ is not None and (t_.dtype != torch.float32 or not t_.is_contiguous()):
+                raise KernelLibraryError(f"qkv_heads: {n_} must be dense float32")
+        if cos.shape[1] * 2 != rotary_dim or positions.dtype != torch.int32:
+            raise KernelLibraryError("qkv_heads: table width does not match rotary_dim, or positions are not int32")
+        page_size = num_pages = stride = 0
+        if write_kv:
+            if (k_pages.dtype != torch.bfloat16 or k_pages.shape != v_pages.shape or not k_pages.is_contiguous() or not v_pages.is_contiguous()
+                    or (k_pages.shape[1], k_pages.shape[3]) != (n_kv_heads, head_dim) or block_table.dtype != torch.int32
+                    or token_seq.dtype != torch.int32 or not block_table.is_contiguous()):
+                raise KernelLibraryError(f"qkv_heads: pages {tuple(k_pages.shape)} or tables do not fit {n_kv_heads} heads of {head_dim}")
+            num_pages, page_size, stride = k_pages.shape[0], k_pages.shape[2], block_table.shape[1]
+        st = status if status is not None else tc_status(x.device)
+        check(_l.library().pb_gemm_pair_heads_bf16(
+            x.data_ptr(), w.data_ptr(), T, x.shape[1], x.stride(0), w.stride(0), out.data_ptr(),
+            k_pages.data_ptr() if write_kv else None, v_pages.data_ptr() if write_kv else None,
+            None if q_weight is None else q_weight.data_ptr(), None if k_weight is None else k_weight.data_ptr(), float(eps),
+            cos.data_ptr(), sin.data_ptr(), cos.shape[0], positions.data_ptr(), token_seq.data_ptr() if write_kv else None,
+            block_table.data_ptr() if write_kv else None, stride, page_size, num_pages, n_heads, n_kv_heads if write_kv else 0,
+            head_dim, 1 if (write_kv and K.kv_swizzled(x.dtype, head_dim)) else 0, 0, st.data_ptr(), _l.current_stream_ptr(x.device)),
+            "gemm_pair (q/k/v)")
+        return out
+    qkv = linear(x, w, None if bias is None else bias[:rows])
+    return K.qknorm_rope_kvwrite(qkv, n_heads, n_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin, rotary_dim, positions,
+                                 token_seq, block_table, k_pages, v_pages, write_kv, status, out=out, interleaved=interleaved)
 
 
 _tc_status: Dict[torch.device, torch.Tensor] = {}

@@ -19,7 +19,7 @@ import torch
 from ..config.spec import AttentionSpec
 from ..ops import kernels as K
 from ..ops.attention import paged_attention
-from ..ops.linear import linear
+from ..ops.linear import linear, qkv_heads
 from ..weights.loader import TensorReq
 from .registry import KvPagesNeed, RunContext, make_part, register_part
 
@@ -90,17 +90,15 @@ class Attention:
     # -- one step -----------------------------------------------------------------
     def forward(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
         s = self.spec
-        if write_cache:
-            qkv = linear(x, self.w_qkv, self.b_qkv)
-        else:
-            qkv = linear(x, self.w_qkv[:self.q_cols], None if self.b_qkv is None else self.b_qkv[:self.q_cols])
         table = batch.block_tables[cache.group]
-        q = K.qknorm_rope_kvwrite(
-            qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm,
+        # the projection, the per-head norms, the rotation and the cache write: one call, which for a prompt step's
+        # many rows is one kernel (the product with the rest in its epilogue), else the product and a kernel behind it
+        q = qkv_heads(
+            x, self.w_qkv, self.b_qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm,
             s.qk_norm_eps if s.qk_norm_eps is not None else 0.0, self.position.cos, self.position.sin,
-            self.position.rotary_dim, batch.positions, batch.table_row_of_token, table, cache.k_pages, cache.v_pages,
-            write_cache, batch.status, out=batch.workspace("attention_q", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype),
-            interleaved=bool(getattr(self.position, "interleaved", False)))
+            self.position.rotary_dim, bool(getattr(self.position, "interleaved", False)), batch.positions,
+            batch.table_row_of_token, table, cache.k_pages, cache.v_pages, write_cache, batch.status,
+            out=batch.workspace("attention_q", (batch.n_tokens, s.num_heads, s.head_dim), x.dtype))
         o = paged_attention(q, cache.k_pages, cache.v_pages, batch, cache.group, s.softmax_scale, s.window,
-                            out=batch.workspace("attention_out", (batch.n_tokens, s.num_heads, s.head_dim), qkv.dtype))
+                            out=batch.workspace("attention_out", (batch.n_tokens, s.num_heads, s.head_dim), x.dtype))
         return linear(o.view(batch.n_tokens, self.q_cols), self.w_o, self.b_o)

@@ -727,6 +727,59 @@ def test_gemm_pair_gated(M, I, K_):
     assert int(tc_status(x.device).item()) == 0
 
 
+@pytest.mark.parametrize("nH,nKV,D", [(32, 8, 128), (5, 1, 64), (6, 2, 64), (3, 1, 256), (9, 3, 128)])
+@pytest.mark.parametrize("norm", [True, False])
+def test_gemm_pair_with_heads_epilogue(nH, nKV, D, norm):
+    # The merged q/k/v projection with norm, rotation and cache write in the product's epilogue against the product
+    # followed by the kernel that the tests above hold against the formulas: the same queries and the same pages
+    # within the rounding of the projection to bfloat16 that the one-kernel form leaves out; tiles that end inside
+    # the heads' columns, padding rows of a captured step, a token without a page, a position outside the tables.
+    from prelude_b200.ops.linear import qkv_heads
+    T, H, page, eps, theta = 600, 328, 16, 1e-6, 10000.0
+    x = rnd(T, H, dtype=torch.bfloat16, seed=61)
+    w = rnd((nH + 2 * nKV) * D, H, dtype=torch.bfloat16, seed=62, scale=0.06)
+    qw, kw = (1 + 0.2 * rnd(D, seed=2), 1 + 0.2 * rnd(D, seed=3)) if norm else (None, None)
+    inv = torch.tensor([1.0 / theta ** (i / D) for i in range(0, D, 2)], dtype=torch.float64).float()
+    ang = torch.arange(400, dtype=torch.float32)[:, None] * inv[None]
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    lens = [290, 200, 100]
+    pos = torch.cat([torch.arange(n) for n in lens] + [torch.zeros(10, dtype=torch.long)]).to(torch.int32).to(DEV)
+    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)] + [torch.full((10,), -1)]).to(torch.int32).to(DEV)
+    per = -(-max(lens) // page)
+    num_pages = 3 * per + 5
+    table = torch.randperm(num_pages, generator=torch.Generator().manual_seed(9)).to(torch.int32)[:3 * per].reshape(3, per).to(DEV)
+    live = seq >= 0
+
+    def run(fused, table_, pos_, write_kv=True):
+        kp = torch.zeros(num_pages, nKV, page, D, dtype=torch.bfloat16, device=DEV)
+        vp = torch.zeros_like(kp)
+        st = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.zeros(T, nH, D, dtype=torch.bfloat16, device=DEV)
+        qkv_heads(x, w, None, nH, nKV, D, qw, kw, eps, cos, sin, D, False, pos_, seq if write_kv else None, table_ if write_kv else None,
+                  kp if write_kv else None, vp if write_kv else None, write_kv, st, out, force=fused)
+        return out, kp, vp, int(st.item())
+
+    one, two = run(True, table, pos), run(False, table, pos)
+    assert one[3] == 0 and two[3] == 0
+    scale = float(two[0].float().abs().max())
+    for a, b in ((one[0][live], two[0][live]), (one[1], two[1]), (one[2], two[2])):
+        assert (a.float() - b.float()).abs().max() <= tol(torch.bfloat16, scale)
+    assert float(one[1].abs().max()) > 0 and float(one[2].abs().max()) > 0
+    assert torch.equal(one[1] == 0, two[1] == 0) or float(((one[1] == 0) != (two[1] == 0)).float().mean()) < 1e-3   # the same places written
+    assert torch.equal(one[0][~live], torch.zeros_like(one[0][~live]))                 # padding rows store nothing
+    assert torch.equal(run(True, table, pos)[0], one[0])
+    q_only = run(True, table, pos, write_kv=False)
+    assert q_only[3] == 0 and torch.equal(q_only[0][live], one[0][live])
+    bad = table.clone()
+    bad[1, 3] = num_pages + 7
+    b1, b2 = run(True, bad, pos), run(False, bad, pos)
+    assert b1[3] == 2 and b2[3] == 2
+    assert torch.equal(b1[1] == 0, b2[1] == 0) or float(((b1[1] == 0) != (b2[1] == 0)).float().mean()) < 1e-3
+    far = pos.clone()
+    far[5] = 400                                                                       # outside the tables
+    assert run(True, table, far)[3] != 0 and run(False, table, far)[3] != 0
+
+
 def test_gemm_pair_finds_the_one_weight_that_matters():
     # one large product at chosen places of M, N and K, everything else small: a lost stage, row or column shows
     from prelude_b200.ops.linear import gemm_pair

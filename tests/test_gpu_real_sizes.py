@@ -163,6 +163,34 @@ def test_every_way_of_cutting_at_real_layer_sizes(name, monkeypatch):
         assert pair_rows and max(pair_rows) >= LN.PAIR_MIN_ROWS
 
 
+def test_a_long_prompt_through_the_fused_products_and_decoding_behind_it(monkeypatch):
+    """1,600 tokens in one step at Qwen3-4B sizes in bfloat16: the merged q/k/v projection with norm, rotation and
+    cache write in its epilogue and the gate/up projection with its activation (both on the paired-block tcgen05
+    kernel), then four tokens one by one that read the pages which that epilogue wrote; logits at the prompt's
+    first, middle and last position and at every decoded one against the plain implementation in float64."""
+    from prelude_b200.ops import linear as LN
+    s = _sized("4b")
+    V = s.cfg["vocab_size"]
+    T, tail = 1600, 4
+    assert T >= LN.PAIR_QKV_MIN_ROWS and LN.PREFILL_GEMM != "cublas"
+    toks = _ids(T + tail, V, 4242)
+    rows = [0, T // 2 - 1, T - 1] + list(range(T, T + tail))
+    ref = forward_logits(s.cfg, s.weights(torch.float64), toks, dtype=torch.float64, rows=rows)
+    schedule = [([("long", toks[:T], [0, T // 2 - 1, T - 1])], [])]
+    schedule += [([("long", [toks[T + i]], [0])], ["long"] if i == tail - 1 else []) for i in range(tail)]
+    runner = _runner(s.model(torch.bfloat16), harness.peak_tokens(schedule, PAGE) // PAGE)
+    taken = []
+    fused = LN.qkv_heads
+    monkeypatch.setattr("prelude_b200.parts.attention.qkv_heads",
+                        lambda x, *a, **k: (taken.append(x.shape[0]), fused(x, *a, **k))[1])
+    got = harness.run_schedule(runner, schedule)
+    assert T in taken
+    worst = _check(got, {"long": {pos: ref[i] for i, pos in enumerate(rows)}}, torch.bfloat16, "4b long prompt")
+    print(f"4b bfloat16 long prompt: worst {worst[0]:.3e} (rms {worst[1]:.3e})")
+    runner.cache.check()
+    assert runner.cache.used_pages() == 0
+
+
 @pytest.mark.parametrize("batch", [1, 8, 17])
 def test_captured_decode_steps_at_real_layer_sizes(batch):
     """The captured decode step and the queued runs of it, through ``Engine`` in bfloat16, at batch 1, 8 (streaming
