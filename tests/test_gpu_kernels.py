@@ -631,6 +631,32 @@ def test_tensor_core_attention_finds_the_one_key_that_matters(monkeypatch, decod
     assert (got.float() - ref.float()).abs().max() <= tol(torch.bfloat16, 4.0)
 
 
+@pytest.mark.parametrize("qn", [1, 130], ids=["decode", "portion"])
+@pytest.mark.parametrize("target", [2, 16384, 33000 - 131])
+def test_tensor_core_attention_finds_the_one_key_that_matters_in_a_long_context(qn, target):
+    # 33,000 keys, 2,063 pages in a scrambled order: the planner's own splits and clusters for the decode kernel, a
+    # block table far longer than the window of it that the prompt kernel keeps in registers; one key (an early
+    # one, one at 16,384, the last that the portion's first query may see)
+    # carries all the weight of the last query's heads
+    from prelude_b200.ops.attention import paged_attention
+    nH, nKV, D, page, L = 8, 2, 128, 16, 33000
+    batch, ks, vs, kp, vp = _batch_for([(L, qn)], page, L // page + 8, nKV, D, seed=6)
+    unit = torch.zeros(D, device=DEV)
+    unit[9] = 1.0
+    q = rnd(qn, nH, D, dtype=torch.bfloat16, seed=5, scale=0.05)
+    q[-1] = (unit * 30).to(torch.bfloat16)
+    q[0] = (unit * 30).to(torch.bfloat16)
+    kp[:, :, :, :] = (kp.float() * 0.05).to(torch.bfloat16)
+    pg = int(batch.block_tables[0][0, target // page])
+    _put(kp, pg, target % page, (unit * 30).to(torch.bfloat16).expand(nKV, D))      # score 900 / sqrt(128) = 80 against ~0
+    got = paged_attention(q, kp, vp, batch, 0, 1 / math.sqrt(D), None)
+    assert (got[-1, 0].float() - vs[0][target, 0].float()).abs().max() < 0.06
+    if target <= L - qn:                                   # the portion's first query sees it too
+        assert (got[0, 3].float() - vs[0][target, 0].float()).abs().max() < 0.06
+    ref = K().paged_attention_ref(q, kp, vp, batch.positions, batch.token_seq, batch.block_tables[0], 1 / math.sqrt(D), None)
+    assert (got.float() - ref.float()).abs().max() <= tol(torch.bfloat16, 4.0)
+
+
 def test_tensor_core_attention_refuses_or_falls_back():
     from prelude_b200.ops.attention import tensor_core_shape_ok
     assert tensor_core_shape_ok(32, 8, 128, True) and tensor_core_shape_ok(64, 1, 128, False)
