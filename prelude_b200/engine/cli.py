@@ -73,6 +73,8 @@ def build_parser() -> argparse.ArgumentParser:
                     help="Largest decode batch that is captured as a CUDA graph (env PRELUDE_CUDA_GRAPH_MAX_BS)")
     ap.add_argument("--max-model-len", type=int, default=0, help="Cap on a request's length; 0 = max_position_embeddings")
     # the request(s)
+    ap.add_argument("--random-weights", action="store_true",
+                    help="Read config.json alone from --model and draw the weights from --seed on the device")
     ap.add_argument("--prompt-ids", action="append", default=[],
                     help="A prompt as comma-separated token ids (repeatable)")
     ap.add_argument("--prompt-file", help="File with one prompt per line: comma- or space-separated token ids")
@@ -125,7 +127,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                         max_total_tokens=args.max_total_tokens, decode_reservation_cap=args.decode_reservation_cap,
                         decode_priority_max_remaining_tokens=args.decode_priority_max_remaining_tokens,
                         cuda_graph=args.cuda_graph, cuda_graph_max_bs=args.cuda_graph_max_bs,
-                        max_model_len=args.max_model_len or None)
+                        max_model_len=args.max_model_len or None,
+                        random_weights_seed=args.seed if args.random_weights else None)
         params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k or None,
                                 seed=args.seed, max_new_tokens=args.max_new_tokens,
                                 stop_token_ids=tuple(_parse_ids(args.stop_token_ids)), ignore_eos=args.ignore_eos)

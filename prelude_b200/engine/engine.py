@@ -87,9 +87,10 @@ class Engine:
                  max_running_requests: int = 256, max_num_batched_tokens: int = 8192,
                  long_prefill_token_threshold: int = 0, max_total_tokens: int = 0, decode_reservation_cap: int = 0,
                  decode_priority_max_remaining_tokens: int = 4, cuda_graph: bool = True, cuda_graph_max_bs: int = 64,
-                 max_model_len: Optional[int] = None, decode_burst: int = 8):
+                 max_model_len: Optional[int] = None, decode_burst: int = 8, random_weights_seed: Optional[int] = None):
         """``model`` is a folder with config.json and safetensors files (or a
-        DecoderModel that is already on the device).
+        DecoderModel that is already on the device).  With ``random_weights_seed`` the folder's
+        config.json alone is read and the weights are drawn from that seed on the device.
 
         ``num_pages`` fixes the cache size; without it the cache takes what
         ``gpu_memory_utilization`` of the device leaves after the weights and a
@@ -107,7 +108,7 @@ class Engine:
             self.device, self.dtype = model.ctx.device, model.ctx.dtype
         else:
             self.config = load_model_config(model)
-            self.model = load_model(model, self.dtype, self.device)
+            self.model = load_model(model, self.dtype, self.device, random_weights_seed=random_weights_seed)
         spec = self.model.spec
         self.max_model_len = min(max_model_len or spec.max_positions, spec.max_positions)
         needs = self.model.cache_needs()

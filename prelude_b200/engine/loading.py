@@ -34,10 +34,20 @@ def parse_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
 
 
 def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
-               device: Union[str, torch.device] = "cuda:0") -> DecoderModel:
-    """config.json -> registry -> typed configuration -> model spec -> parts -> weights by name."""
+               device: Union[str, torch.device] = "cuda:0", random_weights_seed: Optional[int] = None) -> DecoderModel:
+    """config.json -> registry -> typed configuration -> model spec -> parts -> weights by name.  With
+    ``random_weights_seed`` the folder needs its config.json only: the tensors the model asks for are drawn on the
+    device (linear ~N(0, 0.02), norm scales 1 + U(-0.05, 0.05), each tensor seeded by (seed, name)) and go through
+    the same loading by name."""
     config = load_model_config(model_dir)
-    store = WeightStore.open(model_dir)
+    if random_weights_seed is not None:
+        from ..weights.random_init import random_tensors
+        run_dtype = parse_dtype(dtype)
+        tensors = random_tensors(config, seed=int(random_weights_seed), std=0.02, norm_jitter=0.05,
+                                 dtype=torch.bfloat16 if run_dtype == torch.bfloat16 else torch.float32, device=device)
+        store = WeightStore.from_tensors(tensors)
+    else:
+        store = WeightStore.open(model_dir)
     return build_model(config.to_model_spec(), store, dtype, device)
 
 

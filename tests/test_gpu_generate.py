@@ -182,6 +182,30 @@ def test_command_line(folders):
     assert bad.returncode != 0 and "no cpu path" in bad.stderr
 
 
+def test_random_weights_from_a_seed_need_the_configuration_alone(folders, tmp_path):
+    # a folder with config.json and nothing else: --random-weights draws the tensors the model asks for from --seed
+    # on the device; the same seed gives the same tokens, through the command line and through the entry point
+    import shutil
+    from prelude_b200 import Engine
+    from prelude_b200.weights.random_init import random_tensors
+    bare = tmp_path / "bare"
+    bare.mkdir()
+    shutil.copy(os.path.join(folders["B"], "config.json"), bare / "config.json")
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "prelude"), "--model", str(bare), "--dtype", "f32", "--random-weights",
+           "--seed", "7", "--prompt-ids", "5,17,3,9", "--max-new-tokens", "6", "--temperature", "0", "--num-pages", "16", "--ignore-eos"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    tokens = json.loads(out.stdout.strip().splitlines()[0])["token_ids"]
+    eng = Engine(str(bare), dtype="f32", num_pages=16, random_weights_seed=7)
+    assert eng.generate([5, 17, 3, 9], temperature=0.0, max_new_tokens=6, ignore_eos=True).token_ids == tokens
+    # and they are the plain implementation's tokens for those tensors
+    cfg = json.load(open(bare / "config.json"))
+    w = {k: v.cpu() for k, v in random_tensors(cfg, seed=7, std=0.02, norm_jitter=0.05, dtype=torch.float32, device="cuda:0").items()}
+    assert tokens == greedy_generate(cfg, w, [5, 17, 3, 9], 6)
+    missing = subprocess.run(cmd[:6] + cmd[7:], capture_output=True, text=True, timeout=600)       # without --random-weights
+    assert missing.returncode != 0 and "safetensors" in missing.stderr
+
+
 def test_a_generation_that_fails_gives_its_pages_back(folders, monkeypatch):
     # a step that raises in the middle of a generation: the call raises, nothing stays held, the engine goes on
     cfg, w = tiny.PARAMS["A"][0], tiny.read_weights(folders["A"])
