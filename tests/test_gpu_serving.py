@@ -148,3 +148,63 @@ def test_results_of_requests_that_are_not_generates_own_are_kept(folder):
     assert eng.result(other).token_ids == want[1] and eng.result(other) is None
     with pytest.raises(TypeError):
         eng.submit(prompts[0], temperatur=0.0)
+
+
+@pytest.mark.parametrize("burst,pages,seed", [(6, 72, 1), (1, 18, 5), (8, 24, 9)])
+def test_random_arrivals_aborts_sampling_and_page_pressure(folder, burst, pages, seed):
+    """Some hundred requests that come at random steps, a few of them aborted at random moments, a fifth of them
+    sampled (with and without filters) beside the greedy ones, a pool small enough in two of the three runs that
+    requests are preempted: every greedy request that finishes has the tokens it gets alone from the plain
+    implementation (an aborted one a prefix of them), nothing is held at the end.  Where a token differs, the plain
+    implementation's float64 logits of the two candidates must be a tie (within 5e-5): among thousands of tokens of a
+    flat random model that happens."""
+    import random
+    from plain.qwen3_plain import forward_logits
+    cfg, w = tiny.PARAMS["B"][0], tiny.read_weights(folder)
+    v = cfg["vocab_size"]
+    rng = random.Random(seed)
+    eng = _engine(folder, page_size=8, num_pages=pages, max_running_requests=6, max_num_batched_tokens=24, decode_burst=burst)
+    cache, live = {}, {}
+    submitted = checked = ties = aborted = steps = 0
+
+    def plain(p, n):
+        key = (tuple(p), n)
+        if key not in cache:
+            cache[key] = greedy_generate(cfg, w, p, n)
+        return cache[key]
+
+    while submitted < 160 or eng.has_work():
+        if submitted < 160 and rng.random() < 0.35 and len(live) < 14:
+            p = tiny.random_ids(rng.choice([1, 2, 3, 7, 8, 9, 15, 16, 17, 30, 45, 64, 90]), v, rng.randrange(1 << 20))
+            new, greedy = rng.choice([1, 2, 5, 9, 16, 25]), rng.random() < 0.8
+            extra = {} if greedy else {"top_k": rng.choice([None, 5]), "top_p": rng.choice([1.0, 0.9])}
+            rid = eng.submit(p, temperature=0.0 if greedy else 0.9, seed=rng.randrange(1000), max_new_tokens=new, ignore_eos=True, **extra)
+            live[rid] = (p, new, greedy)
+            submitted += 1
+        if live and rng.random() < 0.05:
+            eng.abort(rng.choice(list(live)))
+        for r in eng.step_once():
+            p, new, greedy = live.pop(r.request_id)
+            if r.finish_reason == "cache_full":
+                continue
+            if r.finish_reason == "abort":
+                aborted += 1
+            else:
+                assert r.finish_reason == "length" and len(r.token_ids) == new
+            if greedy:
+                want = plain(p, new)[:len(r.token_ids)]
+                if r.token_ids != want:
+                    k = next(i for i in range(len(want)) if r.token_ids[i] != want[i])
+                    lg = forward_logits(cfg, w, p + want[:k], dtype=torch.float64)[-1]
+                    assert abs(float(lg[want[k]] - lg[r.token_ids[k]])) < 5e-5, (r.request_id, k, r.token_ids, want)
+                    ties += 1
+                checked += 1
+        steps += 1
+        assert steps < 20000
+        if steps % 100 == 0:
+            eng.cache.check()
+    eng.cache.check()
+    assert eng.cache.used_pages() == 0 and not eng.cache.requests and not live
+    assert checked > 80 and ties <= 2 and aborted > 0
+    if pages < 30:
+        assert eng.stats().preemptions > 0
