@@ -30,10 +30,11 @@
 // the parts of a split tile summed through the L2 cache, was measured: the products are bound by power here, not by
 // idle pairs - 64 pairs take as long as 74 - and the summing cost 10 us, so it did not pay.)
 //
-// In each block: warp 4 issues the tensor-map copies of its halves (six 32 KB stages), warp 5 of the LEADING block
+// In each block: warp 8 issues the tensor-map copies of its halves (six 32 KB stages), warp 9 of the LEADING block
 // issues the products for both and commits to the barriers of both (tcgen05.commit ... multicast::cluster), warps
-// 0..3 read the block's 128 accumulator rows out of tensor memory (two accumulators of 256 columns: one's stores
-// overlap the next one's products) and store.  Every wait is bounded in time; a block that gives up raises the
+// 0..7 read the block's 128 accumulator rows out of tensor memory (two accumulators of 256 columns: one's stores
+// overlap the next one's products; a warp reads the lanes of its number modulo four, so two warps share a row's
+// columns) and store.  Every wait is bounded in time; a block that gives up raises the
 // status word, and both blocks leave through the cluster's last barrier with their tensor memory freed.
 #include "tcgen05.cuh"
 
@@ -45,7 +46,8 @@ namespace cg = cooperative_groups;
 #define GP_HALF 128
 #define GP_BK 64
 #define GP_STAGES 6
-#define GP_THREADS 192
+#define GP_THREADS 320                  // eight epilogue warps, one that copies, one that issues the products
+#define GP_EPI_WARPS 8
 #define GP_A_BYTES (GP_BM * GP_BK * 2)              // a stage's tile of A in one block
 #define GP_STAGE_BYTES (2 * GP_A_BYTES)             // and as much of B
 
@@ -116,6 +118,7 @@ __device__ __forceinline__ uint32_t gp_idesc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GP_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
+__device__ __forceinline__ void gp_bar_epilogue() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
 // 32 columns of this thread's row of the accumulator
 __device__ __forceinline__ void gp_row_chunk(uint32_t taddr, float* v) {
     uint32_t r[32];
@@ -162,7 +165,7 @@ __device__ __forceinline__ void gp_store_head_chunks(__nv_bfloat16* row, int col
 // The epilogue of the q/k/v form for one tile: this thread's token, the 256 / head_dim heads of the tile.
 // (Norm, rotation and the cache write as crates/prelude-core/src/models/qwen3.rs:161-231 orders them; the same
 // arithmetic as the kernel in rope_kv.cu, on the float32 sums instead of their bfloat16 rounding.)
-__device__ __forceinline__ void gp_heads_epilogue(const GpParams& p, uint32_t taddr, int tn, int t, bool live) {
+__device__ __forceinline__ void gp_heads_epilogue(const GpParams& p, uint32_t taddr, int tn, int t, bool live, int side) {
     const GpHeads& r = p.heads;
     const int D = r.head_dim, half = D >> 1;
     const int pos = live ? r.positions[t] : 0;
@@ -173,7 +176,10 @@ __device__ __forceinline__ void gp_heads_epilogue(const GpParams& p, uint32_t ta
     size_t page_row = 0;
     int in_page = 0;
     const int heads_per_tile = GP_BN / D, total_heads = r.n_heads + 2 * r.n_kv_heads;
-    for (int hh = 0; hh < heads_per_tile; ++hh) {
+    // the tile's heads are shared out between the two sets of epilogue warps (a single 256-wide head goes to the first)
+    const int per_side = heads_per_tile > 1 ? heads_per_tile / 2 : 1;
+    if (heads_per_tile == 1 && side == 1) return;
+    for (int hh = side * per_side; hh < (side + 1) * per_side; ++hh) {
         const int slot = tn * heads_per_tile + hh;
         if (slot >= total_heads) break;                                     // the same for the whole block
         const bool is_q = slot < r.n_heads, is_k = !is_q && slot < r.n_heads + r.n_kv_heads;
@@ -278,17 +284,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (threadIdx.x == 0) {
         s_ok = 1;
         for (int s = 0; s < GP_STAGES; ++s) { tc_mbar_init(&full_bar[s], 1); tc_mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < 2; ++a) { tc_mbar_init(&acc_full[a], 1); tc_mbar_init(&acc_empty[a], 8); }   // four warps of each block
+        for (int a = 0; a < 2; ++a) { tc_mbar_init(&acc_full[a], 1); tc_mbar_init(&acc_empty[a], 2 * GP_EPI_WARPS); }   // the epilogue warps of both blocks
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 5) gp_tmem_alloc2(&tmem_holder, 512);       // one warp of each block, the same warp in both
-    if (warp == 4 && lane == 0) { tc_prefetch_map(&map_a); tc_prefetch_map(&map_b); }
+    if (warp == 9) gp_tmem_alloc2(&tmem_holder, 512);       // one warp of each block, the same warp in both
+    if (warp == 8 && lane == 0) { tc_prefetch_map(&map_a); tc_prefetch_map(&map_b); }
     tc_fence_before();
     cluster.sync();                                         // both blocks' barriers and tensor memory are set up
     tc_fence_after();
     const uint32_t tmem_base = tmem_holder;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------- copies: this block's 128 rows of A and its 128 rows of B for every stage ----------------
         if (lane == 0) {
             bool ok = true;
@@ -314,7 +320,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
             if (!ok && p.status) atomicExch(p.status, 8);
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------- products: the leading block issues for the pair ----------------
         if (rank == 0) {
             const uint32_t idesc = gp_idesc();
@@ -346,9 +352,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!ok && lane == 0 && p.status) atomicExch(p.status, 9);
         }
     } else {
-        // ---------------- epilogue: four warps, this block's 128 accumulator rows ----------------
+        // ---------------- epilogue: eight warps, this block's 128 accumulator rows ----------------
+        // A warp reads the 32 tensor-memory lanes of its number modulo four; warps 0..3 take the first half of a
+        // tile's columns (features, heads), warps 4..7 the second.
         pb_grid_dep_wait();                                 // the output may still be in use by the kernel before
-        const int row = warp * 32 + lane;                   // row of the block's half = tensor-memory lane
+        const int quarter = warp & 3, side = warp >> 2;
+        const int row = quarter * 32 + lane;                // row of the block's half = tensor-memory lane
         int seg = 0;
         bool ok = true;
         for (int tile = pair; tile < n_tiles; tile += n_pairs, ++seg) {
@@ -356,19 +365,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int acc = seg & 1;
             if (ok) ok = tc_mbar_wait(&acc_full[acc], (seg >> 1) & 1);
             if (!ok) s_ok = 0;
-            tc_bar_epilogue();
+            gp_bar_epilogue();
             if (!s_ok) { ok = false; break; }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + acc * GP_BN + ((uint32_t)(warp * 32) << 16);
+            const uint32_t taddr = tmem_base + acc * GP_BN + ((uint32_t)(quarter * 32) << 16);
             const int gi = tm * 256 + rank * GP_BM + row;
             const bool live = gi < p.rows_a;
             __nv_bfloat16* orow = p.out + (size_t)(live ? gi : 0) * p.ldo;
             if (p.gated == 2) {
-                gp_heads_epilogue(p, taddr, tn, gi, live);
+                gp_heads_epilogue(p, taddr, tn, gi, live, side);
             } else if (p.gated) {
                 const int col0 = tn * GP_HALF;
 #pragma unroll 1
-                for (int c0 = 0; c0 < GP_HALF; c0 += 32) {
+                for (int c0 = side * (GP_HALF / 2); c0 < (side + 1) * (GP_HALF / 2); c0 += 32) {
                     float g[32], up[32];
                     gp_row_chunk(taddr + c0, g);
                     gp_row_chunk(taddr + GP_HALF + c0, up);
@@ -380,7 +389,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             } else {
                 const int col0 = tn * GP_BN;
 #pragma unroll 1
-                for (int c0 = 0; c0 < GP_BN; c0 += 32) {
+                for (int c0 = side * (GP_BN / 2); c0 < (side + 1) * (GP_BN / 2); c0 += 32) {
                     float v[32];
                     gp_row_chunk(taddr + c0, v);
                     if (live && col0 + c0 < p.out_cols) {
@@ -404,7 +413,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // nobody touches the other block's shared memory, barriers or tensor memory after this
     tc_fence_before();
     cluster.sync();
-    if (warp == 5) {
+    if (warp == 9) {
         __syncwarp();
         tc_fence_after();
         gp_tmem_dealloc2(tmem_base, 512);
