@@ -27,7 +27,7 @@ _STATUS = {2: "a token's page id lies outside the pool (cache write)", 3: "a pos
            6: "a page id lies outside the pool (attention)", 7: "an attention kernel gave up waiting for a copy",
            8: "the tensor-core product gave up waiting for a copy", 9: "a tensor-core kernel gave up waiting for its products",
            10: "a tensor-core kernel gave up waiting for its accumulator", 11: "a streaming product's loader gave up waiting for a free stage",
-           12: "a streaming product gave up waiting for its input or weights", 13: "the chained feed-forward gave up waiting at its barrier"}
+           12: "a streaming product gave up waiting for its input or weights"}
 
 
 def status_message(code: int) -> str:
